@@ -1,0 +1,64 @@
+// Shared helpers of the sm_100a kernels: element types, rounding points, reductions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers and a stream, launches
+// asynchronously and returns the launch's cudaError_t as an int (0 = ok). Negative return
+// values are refusals of a size or an alignment that the kernel does not support; the Python
+// side turns both into exceptions, so that a wrong size never gives a wrong result.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum LbDtype { LB_F32 = 0, LB_BF16 = 1 };
+
+// refusals (negative so that they cannot be mistaken for a cudaError_t)
+#define LB_ERR_DTYPE (-1)
+#define LB_ERR_SIZE (-2)
+#define LB_ERR_ALIGN (-3)
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  // value of `v` after a round trip through the storage type
+  static __device__ __forceinline__ float round(float v) { return v; }
+};
+template <> struct Elem<bf16> {
+  static __device__ __forceinline__ float load(const bf16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block in a fixed order (so that a row's result does not depend on the batch):
+// butterfly inside each warp, then warp 0 adds the warps' partial sums in index order.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    scratch[32] = total;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int lb_last_error() { return (int)cudaGetLastError(); }

@@ -1,0 +1,223 @@
+// Row-wise kernels of the decoder: embedding gather, (residual add +) RMSNorm, per-head
+// QK-norm + rotary embedding + KV page write, SwiGLU. Each is templated on the storage type
+// (float for the true 32-bit path, bf16 for serving); all arithmetic is in 32-bit floats and
+// the bf16 instantiation rounds where the reference's bf16 tensors round.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// x[t, :] = table[ids[t], :]   (layover/model.py:219,247: no scaling)
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ x,
+                             int hidden) {
+  const T* src = table + (size_t)ids[blockIdx.x] * hidden;
+  T* dst = x + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+}
+
+LB_EXPORT int lb_embed(int dtype, const int* ids, const void* table, void* x, int tokens, int hidden,
+                       cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dtype == LB_F32)
+    embed_kernel<float><<<tokens, 256, 0, stream>>>(ids, (const float*)table, (float*)x, hidden);
+  else if (dtype == LB_BF16)
+    embed_kernel<bf16><<<tokens, 256, 0, stream>>>(ids, (const bf16*)table, (bf16*)x, hidden);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+// v = x[row] + delta[row] (sum in 32-bit, rounded to T once; written back to x unless rows are
+// picked), out = weight * round_T(v * rsqrt(mean(v^2) + eps))   (layover/model.py:31-36,165-166)
+// With `rows`, output row r reads source row rows[r] and x is not written (final norm of the
+// wanted rows only). The norm weight is always 32-bit.
+template <typename T>
+__global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
+                                   T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  extern __shared__ float row_vals[];  // hidden floats + 33 for the reduction
+  float* scratch = row_vals + hidden;
+  const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  T* xr = x + src * hidden;
+  const T* dr = delta ? delta + src * hidden : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = Elem<T>::load(xr + i);
+    if (dr) {
+      v = Elem<T>::round(v + Elem<T>::load(dr + i));
+      if (!rows) Elem<T>::store(xr + i, v);
+    }
+    row_vals[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    Elem<T>::store(o + i, weight[i] * Elem<T>::round(row_vals[i] * inv));
+}
+
+LB_EXPORT int lb_add_rmsnorm(int dtype, void* x, const void* delta, const float* weight, void* out,
+                             const int* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  if (smem > 200 * 1024) return LB_ERR_SIZE;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (dtype == LB_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>((float*)x, (const float*)delta, weight,
+                                                                   (float*)out, rows, hidden, eps);
+  } else if (dtype == LB_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    add_rmsnorm_kernel<bf16><<<n_rows, threads, smem, stream>>>((bf16*)x, (const bf16*)delta, weight, (bf16*)out,
+                                                                  rows, hidden, eps);
+  } else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- QK-norm + rotary + KV write
+// One warp per (token, head) of the fused projection row [q heads | k heads | v heads] x dim.
+//   q, k: per-head RMSNorm over dim (weight shared by the heads, layover/model.py:124-125), then
+//         x*cos + rotate_half(x)*sin with angle = pos * inv_freq[i], cos/sin rounded to T
+//         (layover/model.py:100-102,127-128,193-197); dims >= 2*n_freq pass through unrotated.
+//   q is written to q_out [tokens, q_heads, dim]; k and v go to their page:
+//         pool[(page * kv_heads + head) * page_tokens + slot][dim], page*page_tokens+slot = slot_map[t]
+//         (layover/model.py:133,139-140).
+// Null norm weights skip the norm, null inv_freq skips the rotation, null pools skip the write
+// (then k is written back in place into the projection row, for a position encoding that runs
+// as a separate step), a null q_out skips the q heads (the pass that only writes pages).
+#define QKV_MAX_PER_LANE 8  // dim <= 256
+template <typename T>
+__global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
+                                       T* __restrict__ v_pool, const float* __restrict__ q_norm_w,
+                                       const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+                                       const int* __restrict__ positions, const int* __restrict__ slot_map,
+                                       int tokens, int q_heads, int kv_heads, int dim, int n_freq, int page_tokens,
+                                       float eps) {
+  const int heads = q_heads + 2 * kv_heads;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= tokens * heads) return;
+  const int t = warp / heads, h = warp % heads;
+  T* src = qkv + ((size_t)t * heads + h) * dim;
+  const bool is_q = h < q_heads, is_k = !is_q && h < q_heads + kv_heads;
+  const int half = dim >> 1;
+
+  T* dst;
+  if (is_q) {
+    if (!q_out) return;  // a second pass that only writes pages
+    dst = q_out + ((size_t)t * q_heads + h) * dim;
+  } else {
+    T* pool = is_k ? k_pool : v_pool;
+    if (pool) {
+      const int kvh = is_k ? h - q_heads : h - q_heads - kv_heads;
+      const int slot = slot_map[t];
+      const size_t page = slot / page_tokens, within = slot % page_tokens;
+      dst = pool + ((page * kv_heads + kvh) * page_tokens + within) * dim;
+    } else {
+      dst = src;
+    }
+  }
+  if (!is_q && !is_k) {  // v: a copy
+    if (dst != src)
+      for (int i = lane; i < dim; i += 32) dst[i] = src[i];
+    return;
+  }
+  // lane holds pairs (i, i + half) for i = lane, lane + 32, ...
+  float lo[QKV_MAX_PER_LANE / 2], hi[QKV_MAX_PER_LANE / 2];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < QKV_MAX_PER_LANE / 2; ++j) {
+    const int i = lane + 32 * j;
+    lo[j] = hi[j] = 0.f;
+    if (i < half) {
+      lo[j] = Elem<T>::load(src + i);
+      hi[j] = Elem<T>::load(src + i + half);
+      ss += lo[j] * lo[j] + hi[j] * hi[j];
+    }
+  }
+  const float* w = is_q ? q_norm_w : k_norm_w;
+  if (w) {
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+    for (int j = 0; j < QKV_MAX_PER_LANE / 2; ++j) {
+      const int i = lane + 32 * j;
+      if (i < half) {
+        lo[j] = Elem<T>::round(w[i] * Elem<T>::round(lo[j] * inv));
+        hi[j] = Elem<T>::round(w[i + half] * Elem<T>::round(hi[j] * inv));
+      }
+    }
+  }
+  const float pos = (float)positions[t];
+#pragma unroll
+  for (int j = 0; j < QKV_MAX_PER_LANE / 2; ++j) {
+    const int i = lane + 32 * j;
+    if (i < half) {
+      float a = lo[j], b = hi[j];
+      if (inv_freq && i < n_freq) {
+        const float angle = pos * inv_freq[i];
+        const float c = Elem<T>::round(cosf(angle)), s = Elem<T>::round(sinf(angle));
+        // rotate_half(x) = (-hi, lo): each product and the sum round to T
+        a = Elem<T>::round(Elem<T>::round(lo[j] * c) + Elem<T>::round(-hi[j] * s));
+        b = Elem<T>::round(Elem<T>::round(hi[j] * c) + Elem<T>::round(lo[j] * s));
+      }
+      Elem<T>::store(dst + i, a);
+      Elem<T>::store(dst + i + half, b);
+    }
+  }
+}
+
+LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool, void* v_pool,
+                                 const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
+                                 const int* positions, const int* slot_map, int tokens, int q_heads, int kv_heads,
+                                 int dim, int n_freq, int page_tokens, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dim % 2 || dim > 32 * QKV_MAX_PER_LANE || 2 * n_freq > dim) return LB_ERR_SIZE;
+  // a rotation pairs i with i + dim/2 only when the rotary part spans the whole head
+  if (inv_freq && 2 * n_freq != dim) return LB_ERR_SIZE;
+  const long warps = (long)tokens * (q_heads + 2 * kv_heads);
+  const int threads = 256;
+  const long blocks = (warps * 32 + threads - 1) / threads;
+  if (dtype == LB_F32)
+    qk_norm_rope_kv_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+        (float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, q_norm_w, k_norm_w, inv_freq, positions,
+        slot_map, tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps);
+  else if (dtype == LB_BF16)
+    qk_norm_rope_kv_kernel<bf16><<<(unsigned)blocks, threads, 0, stream>>>(
+        (bf16*)qkv, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, q_norm_w, k_norm_w, inv_freq, positions, slot_map,
+        tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// out[t, j] = silu(gu[t, j]) * gu[t, inter + j], silu(z) = z / (1 + exp(-z)); silu and the
+// product each round to T (layover/model.py:152-153).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long total, int inter) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long t = idx / inter;
+  const int j = (int)(idx % inter);
+  const float g = Elem<T>::load(gate_up + t * 2 * inter + j);
+  const float u = Elem<T>::load(gate_up + t * 2 * inter + inter + j);
+  const float s = Elem<T>::round(g / (1.0f + expf(-g)));
+  Elem<T>::store(out + idx, s * u);
+}
+
+LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, int inter, cudaStream_t stream) {
+  const long total = (long)tokens * inter;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  if (dtype == LB_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
+  else if (dtype == LB_BF16)
+    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}

@@ -1,0 +1,12 @@
+from .batch import BatchBuilder, BatchCapacity, StepBatch, StepEntry
+from .scheduler import Engine, EngineConfig, Request, RequestTooLarge, State
+
+__all__ = ["BatchBuilder", "BatchCapacity", "StepBatch", "StepEntry", "Engine", "EngineConfig", "Request",
+           "RequestTooLarge", "State", "StepFunction"]
+
+
+def __getattr__(name):
+    if name == "StepFunction":
+        from .step import StepFunction
+        return StepFunction
+    raise AttributeError(name)

@@ -1,0 +1,239 @@
+"""One step's batch as the kernels see it: flat token arrays and per-sequence descriptors.
+
+A step is a list of entries (a live request's cache, its next tokens, the places among them
+whose logits are wanted). Prompt portions of any length and single decoded tokens sit side by
+side; the tokens of all entries are laid end to end:
+
+  token_ids [T], positions [T]        the tokens and their absolute positions
+  cu_q [S + 1]                        entry s owns rows cu_q[s] .. cu_q[s + 1]
+  ctx_len [S]                         the request's length once this step's tokens are in
+  state_slots [S]                     the request's slot of fixed-size state
+  logit_rows [R]                      flat rows whose logits are returned, in entry / want order
+  per paged cache group:
+    block_table [S, W]                page ids, padded with the group's scratch page
+    slot_map [T]                      page * page_tokens + slot where the token's K and V go
+  per query-tile size asked for by a mixer:
+    tile_seq, tile_q0 [tiles]         the list of (entry, first query of the tile)
+
+Everything is int32 and packed into one pinned host buffer, so a step costs one host-to-device
+copy whatever the number of layers (as layover/model.py:6-8 and layover/kv/paged_cache.py:143-152
+do for their two kinds of step). With a `capacity`, the device buffer has a fixed size and
+address (what a captured CUDA graph needs) and unused rows are padded with entries of one token
+that read and write only the scratch page and the scratch slot.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache.manager import CacheManager, SequenceCache
+
+
+@dataclass
+class StepEntry:
+    seq: SequenceCache
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+@dataclass
+class GroupBatch:
+    block_table: torch.Tensor
+    slot_map: torch.Tensor
+
+
+@dataclass
+class QueryTiles:
+    tile_seq: torch.Tensor
+    tile_q0: torch.Tensor
+    count: int
+
+
+@dataclass
+class StepBatch:
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    cu_q: torch.Tensor
+    ctx_len: torch.Tensor
+    state_slots: torch.Tensor
+    logit_rows: torch.Tensor
+    n_logit_rows: int
+    groups: list[GroupBatch]
+    tiles: dict[int, QueryTiles]
+    # host-side facts for planning launches
+    q_lens: list[int]
+    ctx_lens: list[int]
+    max_q_len: int
+    max_ctx: int
+    all_decode: bool
+    real_seqs: int = 0          # entries that are not padding
+
+
+@dataclass(frozen=True)
+class BatchCapacity:
+    """Fixed sizes of a batch whose buffers must not move (a captured decode step)."""
+    seqs: int
+    table_width: int
+
+
+class _Layout:
+    def __init__(self):
+        self.size = 0
+        self.fields: dict[str, tuple[int, tuple[int, ...]]] = {}
+
+    def add(self, name: str, *shape: int) -> None:
+        count = 1
+        for s in shape:
+            count *= s
+        self.fields[name] = (self.size, shape)
+        self.size += -(-max(count, 1) // 4) * 4  # keep every array 16-byte aligned
+
+
+class BatchBuilder:
+    """Packs entries into device arrays with one copy. Keeps a small ring of pinned buffers."""
+
+    def __init__(self, cache: CacheManager, device: torch.device, tile_sizes: tuple[int, ...] = ()):
+        self.cache = cache
+        self.device = torch.device(device)
+        self.tile_sizes = tuple(sorted(set(tile_sizes)))
+        self._ring: list[tuple[torch.Tensor, torch.cuda.Event | None]] = []
+        self._next = 0
+
+    def _pinned(self, size: int) -> tuple[torch.Tensor, int]:
+        if self.device.type != "cuda":
+            return torch.empty(size, dtype=torch.int32), -1
+        if len(self._ring) < 4:
+            self._ring.append((torch.empty(max(size, 4096), dtype=torch.int32, pin_memory=True), None))
+        index = self._next % len(self._ring)
+        self._next += 1
+        buffer, event = self._ring[index]
+        if event is not None:
+            event.synchronize()
+        if buffer.numel() < size:
+            buffer = torch.empty(size * 2, dtype=torch.int32, pin_memory=True)
+        self._ring[index] = (buffer, None)
+        return buffer[:size], index
+
+    def build(self, entries: list[StepEntry], capacity: BatchCapacity | None = None,
+              device_buffer: torch.Tensor | None = None) -> StepBatch:
+        cache, page = self.cache, self.cache.block_tokens
+        if not entries and capacity is None:
+            raise ValueError("a step needs at least one entry")
+        real = len(entries)
+        n_seqs = capacity.seqs if capacity else real
+        if real > n_seqs:
+            raise ValueError(f"{real} entries do not fit a batch of {n_seqs}")
+        q_lens = [len(e.tokens) for e in entries] + [1] * (n_seqs - real)
+        if min(q_lens) < 1:
+            raise ValueError("an entry without tokens")
+        starts = [e.seq.num_tokens for e in entries] + [0] * (n_seqs - real)
+        ctx_lens = [s + n for s, n in zip(starts, q_lens)]
+        n_tokens = sum(q_lens)
+        if capacity and n_tokens != n_seqs:
+            raise ValueError("a fixed-capacity batch holds one token per entry")
+        width = capacity.table_width if capacity else max(1, cache.blocks_for(max(ctx_lens)))
+        n_rows = sum(len(e.want) for e in entries) if not capacity else n_seqs
+
+        layout = _Layout()
+        layout.add("token_ids", n_tokens); layout.add("positions", n_tokens)
+        layout.add("cu_q", n_seqs + 1); layout.add("ctx_len", n_seqs); layout.add("state_slots", n_seqs)
+        layout.add("logit_rows", n_rows)
+        for g in range(len(cache.paged)):
+            layout.add(f"table{g}", n_seqs, width); layout.add(f"slots{g}", n_tokens)
+        tile_lists = {}
+        for size in self.tile_sizes:
+            tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, size)]
+            tile_lists[size] = tiles
+            layout.add(f"tile_seq{size}", len(tiles)); layout.add(f"tile_q0{size}", len(tiles))
+
+        host, ring_index = self._pinned(layout.size)
+        view = host.numpy()
+
+        def put(name, values):
+            offset, _ = layout.fields[name]
+            view[offset:offset + len(values)] = values
+
+        tokens_flat, positions, rows, cu = [], [], [], [0]
+        for index, entry in enumerate(entries):
+            n = len(entry.tokens)
+            for w in entry.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {entry.seq.request_id!r}: wanted place {w} is outside its {n} tokens")
+                rows.append(cu[-1] + w)
+            tokens_flat.extend(entry.tokens)
+            positions.extend(range(starts[index], starts[index] + n))
+            cu.append(cu[-1] + n)
+        for _ in range(n_seqs - real):   # padding rows: token 0 at position 0 of the scratch page
+            tokens_flat.append(0); positions.append(0); cu.append(cu[-1] + 1)
+        if capacity:
+            rows = list(range(n_seqs))
+        put("token_ids", tokens_flat); put("positions", positions); put("cu_q", cu); put("ctx_len", ctx_lens)
+        put("state_slots", [e.seq.slot for e in entries] + [cache.scratch_slot] * (n_seqs - real))
+        put("logit_rows", rows)
+        for g, group in enumerate(cache.paged):
+            scratch = group.scratch_page
+            offset, _ = layout.fields[f"table{g}"]
+            slots = []
+            for index in range(n_seqs):
+                row = view[offset + index * width: offset + (index + 1) * width]
+                row[:] = scratch
+                if index < real:
+                    entry = entries[index]
+                    blocks = entry.seq.tables[g].blocks
+                    needed = cache.blocks_for(ctx_lens[index])
+                    if needed > len(blocks) or needed > width:
+                        raise ValueError(
+                            f"request {entry.seq.request_id!r}: {ctx_lens[index]} tokens need {needed} pages, "
+                            f"its table has {len(blocks)} and the batch is {width} wide")
+                    row[:needed] = blocks[:needed]
+                    for pos in range(starts[index], ctx_lens[index]):
+                        slots.append(blocks[pos // page] * page + pos % page)
+                else:
+                    slots.append(scratch * page)
+            put(f"slots{g}", slots)
+        for size, tiles in tile_lists.items():
+            put(f"tile_seq{size}", [t[0] for t in tiles]); put(f"tile_q0{size}", [t[1] for t in tiles])
+
+        if device_buffer is not None:
+            if device_buffer.numel() < layout.size:
+                raise ValueError("the fixed device buffer is too small for this batch")
+            device = device_buffer[:layout.size]
+            device.copy_(host, non_blocking=True)
+        else:
+            device = host.to(self.device, non_blocking=True)
+        if ring_index >= 0:
+            event = torch.cuda.Event()
+            event.record()
+            self._ring[ring_index] = (self._ring[ring_index][0], event)
+
+        def get(name):
+            offset, shape = layout.fields[name]
+            count = 1
+            for s in shape:
+                count *= s
+            return device[offset:offset + count].view(*shape)
+
+        return StepBatch(
+            n_tokens=n_tokens, n_seqs=n_seqs,
+            token_ids=get("token_ids"), positions=get("positions"), cu_q=get("cu_q"), ctx_len=get("ctx_len"),
+            state_slots=get("state_slots"), logit_rows=get("logit_rows"), n_logit_rows=n_rows,
+            groups=[GroupBatch(get(f"table{g}"), get(f"slots{g}")) for g in range(len(cache.paged))],
+            tiles={size: QueryTiles(get(f"tile_seq{size}"), get(f"tile_q0{size}"), len(tiles))
+                   for size, tiles in tile_lists.items()},
+            q_lens=q_lens, ctx_lens=ctx_lens, max_q_len=max(q_lens), max_ctx=max(ctx_lens),
+            all_decode=max(q_lens) == 1, real_seqs=real,
+        )
+
+    @staticmethod
+    def buffer_size(capacity: BatchCapacity, n_groups: int, tile_sizes: tuple[int, ...]) -> int:
+        """Upper bound of the int32 words a fixed-capacity batch takes."""
+        pad = lambda n: -(-max(n, 1) // 4) * 4
+        s = capacity.seqs
+        total = 2 * pad(s) + pad(s + 1) + 3 * pad(s)
+        total += n_groups * (pad(s * capacity.table_width) + pad(s))
+        total += len(set(tile_sizes)) * 2 * pad(s)
+        return total

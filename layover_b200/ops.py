@@ -1,0 +1,226 @@
+"""The engine's device operations: thin, checked wrappers over the CUDA kernels of `csrc/`.
+
+Every function takes CUDA tensors, launches on torch's current stream and returns without
+synchronising. There is no other implementation behind them: if the kernels cannot be
+compiled or loaded, or a tensor is not on a CUDA device, the call raises. A size or alignment
+that a kernel does not support is refused with a ValueError before or by the launch.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+_REFUSALS = {-1: "unsupported dtype", -2: "unsupported size", -3: "unsupported alignment"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dtype}; the engine runs float32 or bfloat16") from None
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code in _REFUSALS:
+        raise ValueError(f"{what}: {_REFUSALS[code]}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("layover_b200 kernels need CUDA tensors: there is no CPU path")
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str) -> None:
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+_signatures_done: set[str] = set()
+
+
+def _fn(lib_name: str, fn_name: str, argtypes):
+    lib = build.load(lib_name)
+    fn = getattr(lib, fn_name)
+    key = lib_name + "." + fn_name
+    if key not in _signatures_done:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _signatures_done.add(key)
+    return fn
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]]; ids int32 [T], table [V, H], out [T, H]."""
+    _need(ids, torch.int32, "ids"); _need(table, None, "table"); _need(out, table.dtype, "out")
+    fn = _fn("elementwise", "lb_embed", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(table.dtype), _ptr(ids), _ptr(table), _ptr(out), ids.shape[0], table.shape[1], _stream()),
+           "embed")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+    """x += delta (in place, unless `rows` picks source rows), out = rmsnorm(x) * weight.
+
+    x, delta [T, H]; weight float32 [H]; out [T or len(rows), H]."""
+    _need(x, None, "x"); _need(weight, torch.float32, "weight"); _need(out, x.dtype, "out")
+    if delta is not None:
+        _need(delta, x.dtype, "delta")
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if out.shape[0] < n_rows or out.shape[-1] != x.shape[-1] or weight.shape[0] != x.shape[-1]:
+        raise ValueError("add_rmsnorm: shapes do not agree")
+    fn = _fn("elementwise", "lb_add_rmsnorm",
+             [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_rows, x.shape[-1],
+              float(eps), _stream()), "add_rmsnorm")
+    return out
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor | None, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
+                    q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, inv_freq: torch.Tensor | None,
+                    positions: torch.Tensor, slot_map: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int,
+                    page_tokens: int, eps: float) -> None:
+    """Per-head norm and rotation of q and k in a fused projection row, q to q_out, k and v to their pages.
+
+    qkv [T, (q_heads + 2 kv_heads) * dim]; q_out [T, q_heads * dim]; pools [pages, kv_heads, page_tokens, dim]."""
+    tokens = qkv.shape[0]
+    _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions")
+    if q_out is not None:
+        _need(q_out, qkv.dtype, "q_out")
+    if qkv.shape[1] != (q_heads + 2 * kv_heads) * dim:
+        raise ValueError("qk_norm_rope_kv: projection row does not match the head counts")
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
+        if t is not None:
+            _need(t, torch.float32, name)
+    if k_pool is not None:
+        _need(k_pool, qkv.dtype, "k_pool"); _need(v_pool, qkv.dtype, "v_pool"); _need(slot_map, torch.int32, "slot_map")
+    n_freq = 0 if inv_freq is None else inv_freq.shape[0]
+    fn = _fn("elementwise", "lb_qk_norm_rope_kv",
+             [c_int] + [c_void_p] * 9 + [c_int] * 6 + [c_float, c_void_p])
+    _check(fn(dtype_code(qkv.dtype), _ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w),
+              _ptr(k_norm_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_map), tokens, q_heads, kv_heads, dim, n_freq,
+              page_tokens, float(eps), _stream()), "qk_norm_rope_kv")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:], gate_up [T, 2 I], out [T, I]."""
+    _need(gate_up, None, "gate_up"); _need(out, gate_up.dtype, "out")
+    inter = gate_up.shape[1] // 2
+    if gate_up.shape[1] != 2 * inter or out.shape[1] != inter or out.shape[0] != gate_up.shape[0]:
+        raise ValueError("swiglu: shapes do not agree")
+    fn = _fn("elementwise", "lb_swiglu", [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inter, _stream()), "swiglu")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T with 32-bit FFMA accumulation (no tensor cores).
+
+    a and w share a dtype (float32 or bfloat16); out has it too, or float32. Rows may be strided."""
+    if a.dtype != w.dtype or a.dim() != 2 or w.dim() != 2 or out.dim() != 2:
+        raise ValueError("gemm: operands must be 2-D and share a dtype")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise ValueError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise ValueError("gemm: innermost dimension must be contiguous")
+    fn = _fn("gemm_simt", "lb_gemm_simt",
+             [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long, c_void_p])
+    _check(fn(dtype_code(a.dtype), dtype_code(out.dtype), _ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0),
+              w.stride(0), out.stride(0), _stream()), "gemm_simt")
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def attention_simt_block_queries() -> int:
+    lib = build.load("attention_simt")
+    lib.lb_attention_simt_block_queries.restype = c_int
+    return lib.lb_attention_simt_block_queries()
+
+
+def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                   block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, tile_seq: torch.Tensor,
+                   tile_q0: torch.Tensor, n_tiles: int, q_heads: int, kv_heads: int, dim: int, page_tokens: int,
+                   scale: float, window: int = 0) -> torch.Tensor:
+    """Paged causal attention in 32-bit arithmetic for any mix of segment lengths.
+
+    q, out [T, q_heads * dim]; pools [pages, kv_heads, page_tokens, dim]; block_table int32 [S, W];
+    cu_q int32 [S + 1]; ctx_len int32 [S]; (tile_seq, tile_q0) int32 [n_tiles] list the query tiles."""
+    _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pool, q.dtype, "k_pool"); _need(v_pool, q.dtype, "v_pool")
+    for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len), ("tile_seq", tile_seq),
+                    ("tile_q0", tile_q0)):
+        _need(t, torch.int32, name)
+    fn = _fn("attention_simt", "lb_attention_simt",
+             [c_int] + [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
+              block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads,
+              kv_heads, dim, page_tokens, float(scale), int(window), _stream()), "attention_simt")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None, seed_lo: torch.Tensor | None,
+           seed_hi: torch.Tensor | None, step: torch.Tensor | None, tokens: torch.Tensor) -> torch.Tensor:
+    """tokens[r] = argmax(logits[r]) for temperature 0, else a Gumbel-max draw at that temperature.
+
+    logits float32 [R, V] (rows may be strided); temperature float32 [R]; seed_lo, seed_hi, step int32 [R]
+    (read as unsigned); tokens int32 [R]. With temperature None every row is greedy."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("sample: logits must be float32 [rows, vocab] with a contiguous vocabulary")
+    _need(tokens, torch.int32, "tokens")
+    rows, vocab = logits.shape
+    if temperature is not None:
+        _need(temperature, torch.float32, "temperature")
+        for name, t in (("seed_lo", seed_lo), ("seed_hi", seed_hi), ("step", step)):
+            _need(t, torch.int32, name)
+    fn = _fn("sampling", "lb_sample", [c_void_p, c_long, c_int, c_int] + [c_void_p] * 6)
+    _check(fn(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed_lo), _ptr(seed_hi),
+              _ptr(step), _ptr(tokens), _stream()), "sample")
+    return tokens
+
+
+# ------------------------------------------------------------------ the bfloat16 path
+BF16_LIBRARIES = ("elementwise", "gemm_simt", "attention_simt", "sampling")
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T, bfloat16 operands, 32-bit accumulation; out bfloat16 or float32."""
+    return gemm_simt(a, w, out)
+
+
+def attention_bf16_tile_sizes() -> tuple[int, ...]:
+    return (attention_simt_block_queries(),)
+
+
+def attention_bf16(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
+    tiles = batch.tiles[attention_simt_block_queries()]
+    attention_simt(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
+                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)

@@ -1,0 +1,121 @@
+"""Grouped-query attention over the paged cache."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import PagedKVNeed, Part, PartSpec, build_part, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Part):
+    """q/k/v projections without bias, optional per-head RMSNorm of q and k, a position encoding,
+    keys and values written to their pages, causal attention over the block table with scale
+    1/sqrt(head_dim), output projection (layover/model.py:105-142).
+
+    params: hidden, q_heads, kv_heads, head_dim; qk_norm_eps (None: no per-head norm);
+    position (a PartSpec or None); window (None: every earlier key is seen);
+    shares_cache (True: the layer has no k/v projections and attends over another layer's
+    pages); tensor names q, k, v, o, q_norm, k_norm relative to the prefix.
+
+    The three projections are stacked at load into one [(q_heads + 2 kv_heads) head_dim, hidden]
+    matrix (the reference runs three products, layover/model.py:121-123)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("hidden", "q_heads", "kv_heads", "head_dim")
+        p = params
+        self.hidden, self.q_heads, self.kv_heads, self.dim = (int(p[k]) for k in ("hidden", "q_heads", "kv_heads", "head_dim"))
+        if self.q_heads % self.kv_heads:
+            raise ValueError(f"q_heads ({self.q_heads}) must be divisible by kv_heads ({self.kv_heads})")
+        if self.dim % 16:
+            raise ValueError(f"head_dim must be a multiple of 16, got {self.dim}")
+        if self.dim > 256:
+            raise ValueError(f"head_dim up to 256 is supported, got {self.dim}")
+        self.qk_norm_eps = p.get("qk_norm_eps")
+        self.window = p.get("window")
+        self.shares_cache = bool(p.get("shares_cache", False))
+        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.dim)))
+        self.position = build_part("position", p.get("position"), prefix)
+        names = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
+                 "o": "self_attn.o_proj.weight", "q_norm": "self_attn.q_norm.weight",
+                 "k_norm": "self_attn.k_norm.weight"}
+        self.names = {k: prefix + p.get(k, default) for k, default in names.items()}
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    # ---- what it wants
+    def tensor_specs(self):
+        n = self.names
+        specs = [TensorSpec(n["q"], (self.q_heads * self.dim, self.hidden))]
+        if not self.shares_cache:
+            specs += [TensorSpec(n["k"], (self.kv_heads * self.dim, self.hidden)),
+                      TensorSpec(n["v"], (self.kv_heads * self.dim, self.hidden))]
+        specs.append(TensorSpec(n["o"], (self.hidden, self.q_heads * self.dim)))
+        if self.qk_norm_eps is not None:
+            specs.append(TensorSpec(n["q_norm"], (self.dim,), kind="vector", init="ones"))
+            if not self.shares_cache:
+                specs.append(TensorSpec(n["k_norm"], (self.dim,), kind="vector", init="ones"))
+        if self.position is not None:
+            specs += self.position.tensor_specs()
+        return specs
+
+    def cache_need(self):
+        return PagedKVNeed(self.kv_heads, self.dim, self.window)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        if self.shares_cache:
+            self.w_qkv = tensors[n["q"]]
+        else:
+            self.w_qkv = torch.cat((tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"])), dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        if self.qk_norm_eps is not None:
+            self.q_norm_w = tensors[n["q_norm"]]
+            self.k_norm_w = None if self.shares_cache else tensors[n["k_norm"]]
+        if self.position is not None:
+            self.position.bind(tensors, runtime)
+
+    # ---- one step
+    def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        tokens = h.shape[0]
+        own_kv = 0 if self.shares_cache else self.kv_heads
+        group = batch.groups[cache.group]
+        qkv = self.runtime.linear(h, self.w_qkv)
+        q = torch.empty((tokens, self.q_heads * self.dim), dtype=h.dtype, device=h.device)
+        eps = float(self.qk_norm_eps or 0.0)
+        table = self.position.inv_freq() if self.position is not None else None
+        fused = self.position is None or table is not None
+        k_pool, v_pool = (cache.k_pool, cache.v_pool) if own_kv else (None, None)
+        if fused:
+            ops.qk_norm_rope_kv(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, batch.positions,
+                                group.slot_map, self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
+        else:
+            # norm in place, the position encoding as its own step, then the page write
+            ops.qk_norm_rope_kv(qkv, q, None, None, self.q_norm_w, self.k_norm_w, None, batch.positions, None,
+                                self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
+            k_rows = qkv[:, self.q_heads * self.dim:(self.q_heads + own_kv) * self.dim]
+            self.position.apply(q.view(tokens, self.q_heads, self.dim),
+                                k_rows.unflatten(1, (own_kv, self.dim)) if own_kv else None, batch.positions)
+            if own_kv:
+                ops.qk_norm_rope_kv(qkv, None, k_pool, v_pool, None, None, None, batch.positions, group.slot_map,
+                                    self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
+        out = torch.empty_like(q)
+        self.attend(q, cache, batch, group, out)
+        return self.runtime.linear(out, self.w_o)
+
+    def attend(self, q, cache, batch, group, out) -> None:
+        self.runtime.attention(q, cache.k_pool, cache.v_pool, out, group.block_table, batch, self.q_heads,
+                               self.kv_heads, self.dim, cache.page_tokens, self.scale, self.window or 0)
+
+
+def attention_spec(hidden, q_heads, kv_heads, head_dim, qk_norm_eps, theta, window=None, shares_cache=False) -> PartSpec:
+    position = PartSpec("rotary_half", {"dim": head_dim, "theta": theta}) if theta is not None else None
+    return PartSpec("attention", {
+        "hidden": hidden, "q_heads": q_heads, "kv_heads": kv_heads, "head_dim": head_dim,
+        "qk_norm_eps": qk_norm_eps, "position": position, "window": window, "shares_cache": shares_cache,
+    })
