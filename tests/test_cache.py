@@ -1,0 +1,200 @@
+"""The cache manager on the host: no page lost, held twice or freed twice, under random orders of
+requests; windows give pages back; state slots; the batch builder's descriptors."""
+
+import random
+
+import pytest
+import torch
+
+from layover_b200.cache import BlockAllocator, CacheManager, OutOfBlocks
+from layover_b200.engine.batch import BatchBuilder, BatchCapacity, StepEntry
+from layover_b200.parts.base import PagedKVNeed, StateNeed
+
+FULL = PagedKVNeed(2, 16, None)
+WINDOW = PagedKVNeed(2, 16, 10)
+STATE = StateNeed((3, 4), torch.float32)
+
+
+def manager(needs, blocks=12, page=4, device=None, max_requests=6):
+    return CacheManager([(i, n, None) for i, n in enumerate(needs)], blocks, page, torch.float32, device, max_requests)
+
+
+def test_allocator_hands_out_all_or_nothing_and_refuses_double_free():
+    a = BlockAllocator(4)
+    got = a.alloc(3)
+    assert got == [0, 1, 2] and a.num_free == 1
+    with pytest.raises(OutOfBlocks):
+        a.alloc(2)
+    assert a.num_free == 1                      # nothing changed
+    a.free(1)
+    assert a.alloc(1) == [1]                    # the page freed last is used again first
+    a.free(0)
+    with pytest.raises(ValueError, match="not allocated"):
+        a.free(0)
+    with pytest.raises(ValueError, match="outside"):
+        a.free(9)
+    a.check()
+
+
+def test_layers_with_the_same_need_share_a_group_and_others_do_not():
+    m = manager([FULL, WINDOW, FULL, STATE, WINDOW])
+    assert len(m.paged) == 2 and len(m.states) == 1
+    assert m.paged[0].entries == [0, 2] and m.paged[1].entries == [1, 4] and m.states[0].entries == [3]
+    assert (m.view(2).group, m.view(2).layer) == (0, 1)
+    assert m.view(3).kind == "state"
+
+
+def test_an_entry_may_read_another_entrys_pages():
+    m = CacheManager([(0, FULL, None), (1, FULL, None), (2, FULL, 0)], 4, 4, torch.float32, "cpu", 2)
+    assert m.paged[0].pool.shape[0] == 2              # the reader owns no pages
+    reader, owner = m.view(2), m.view(0)
+    assert reader.writes is False and reader.layer == owner.layer
+    assert reader.k_pool.data_ptr() == owner.k_pool.data_ptr()
+    with pytest.raises(ValueError, match="reads the cache"):
+        CacheManager([(0, None, None), (1, FULL, 0)], 4, 4, torch.float32, None, 2)
+
+
+def test_grow_commit_close_and_reuse():
+    m = manager([FULL], blocks=5, page=4)
+    a = m.open("a")
+    m.grow(a, 9); m.commit(a, 9)
+    assert a.tables[0].blocks == [0, 1, 2] and a.num_tokens == 9
+    b = m.open("b")
+    with pytest.raises(OutOfBlocks):
+        m.grow(b, 12)                                # three pages wanted, two free: nothing taken
+    assert m.paged[0].allocator.num_free == 2 and b.tables[0].blocks == []
+    m.grow(b, 8); m.commit(b, 8)
+    m.close(a)
+    c = m.open("c")
+    m.grow(c, 4)
+    assert c.tables[0].blocks == [2]                 # a's last page, used again
+    m.check()
+    with pytest.raises(ValueError, match="closed before"):
+        m.close(a)
+    with pytest.raises(ValueError, match="already open"):
+        m.open("b")
+    m.close(b); m.close(c)
+    assert m.num_free == 5
+    m.check()
+
+
+def test_a_window_gives_pages_back_and_takes_them_again():
+    m = manager([WINDOW], blocks=6, page=4)     # window 10: a query at p sees keys > p - 10
+    s = m.open("s")
+    held_most = 0
+    for total in range(1, 60):
+        m.grow(s, total); m.commit(s, total)
+        table = s.tables[0]
+        first_needed = max(0, total - 10 + 1) // 4
+        assert table.first_live == first_needed
+        assert all(b == m.paged[0].scratch_page for b in table.blocks[:first_needed])
+        assert all(b != m.paged[0].scratch_page for b in table.blocks[first_needed:])
+        held_most = max(held_most, m.paged[0].allocator.num_used)
+        m.check()
+    assert held_most <= 4                            # 60 tokens would need 15 pages without the window
+    assert held_most <= m.peak_blocks(0, 60, 1)
+    m.close(s)
+    assert m.num_free == 6
+
+
+def test_a_long_portion_through_a_window_skips_pages_nobody_will_read():
+    m = manager([WINDOW], blocks=8, page=4)
+    s = m.open("s")
+    m.grow(s, 3); m.commit(s, 3)
+    m.grow(s, 30)                                    # 27 tokens at once: every page is still needed in this step
+    assert m.paged[0].allocator.num_used == 8
+    m.commit(s, 30)                                  # afterwards only keys >= 21 matter
+    assert s.tables[0].first_live == 5 and m.paged[0].allocator.num_used == 3
+    m.check_tables(s)
+    m.close(s)
+    assert m.num_free == 8
+
+
+def test_state_slots_are_zeroed_and_reused():
+    m = manager([STATE, FULL], blocks=4, page=4, device="cpu", max_requests=2)
+    a = m.open("a"); b = m.open("b")
+    assert {a.slot, b.slot} == {0, 1}
+    with pytest.raises(OutOfBlocks, match="request slots"):
+        m.open("c")
+    m.view(0).state[a.slot] += 5.0
+    m.close(a)
+    c = m.open("c")
+    assert c.slot == a.slot and float(m.view(0).state[c.slot].abs().sum()) == 0.0
+    assert m.states[0].pool.shape == (1, 3, 3, 4)     # entries, slots + scratch, shape
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_orders_of_requests_lose_no_page(seed):
+    rng = random.Random(seed)
+    m = manager([FULL, WINDOW, FULL], blocks=rng.choice([6, 9, 16]), page=rng.choice([2, 4]), max_requests=5)
+    live, closed = {}, 0
+    for op in range(600):
+        choice = rng.random()
+        if choice < 0.25 and len(live) < 5:
+            name = f"r{op}"
+            live[name] = m.open(name)
+        elif choice < 0.85 and live:
+            name = rng.choice(sorted(live))
+            seq = live[name]
+            new_total = seq.num_tokens + rng.choice([1, 1, 1, 2, 5, 11])
+            before = [g.allocator.num_free for g in m.paged]
+            try:
+                m.grow(seq, new_total)
+            except OutOfBlocks:
+                assert [g.allocator.num_free for g in m.paged] == before   # all or nothing, over all groups
+            else:
+                m.commit(seq, new_total)
+        elif live:
+            name = rng.choice(sorted(live))
+            m.close(live.pop(name)); closed += 1
+        m.check()
+        for seq in live.values():
+            m.check_tables(seq)
+    for seq in live.values():
+        m.close(seq)
+    m.check()
+    assert all(g.allocator.num_free == g.allocator.num_blocks for g in m.paged) and closed > 0
+
+
+def test_batch_descriptors():
+    m = manager([FULL, WINDOW], blocks=10, page=4, device="cpu")
+    a, b = m.open("a"), m.open("b")
+    m.grow(a, 6); m.commit(a, 6)
+    entries = [StepEntry(a, [7, 8, 9], [0, 2]), StepEntry(b, [1] * 5, [4])]
+    for e in entries:
+        m.grow(e.seq, e.seq.num_tokens + len(e.tokens))
+    batch = BatchBuilder(m, "cpu", (2, 4)).build(entries)
+    assert batch.token_ids.tolist() == [7, 8, 9, 1, 1, 1, 1, 1]
+    assert batch.positions.tolist() == [6, 7, 8, 0, 1, 2, 3, 4]
+    assert batch.cu_q.tolist() == [0, 3, 8] and batch.ctx_len.tolist() == [9, 5]
+    assert batch.logit_rows.tolist() == [0, 2, 7] and batch.n_logit_rows == 3
+    assert batch.state_slots.tolist() == [a.slot, b.slot]
+    table = batch.groups[0].block_table
+    assert table.shape == (2, 3) and table[0].tolist() == a.tables[0].blocks[:3]
+    assert table[1].tolist() == b.tables[0].blocks[:2] + [m.paged[0].scratch_page]
+    pages = a.tables[0].blocks
+    assert batch.groups[0].slot_map.tolist()[:3] == [pages[1] * 4 + 2, pages[1] * 4 + 3, pages[2] * 4 + 0]
+    tiles = batch.tiles[2]
+    assert list(zip(tiles.tile_seq.tolist(), tiles.tile_q0.tolist())) == [(0, 0), (0, 2), (1, 0), (1, 2), (1, 4)]
+    assert batch.tiles[4].count == 3 and not batch.all_decode and batch.max_ctx == 9
+    with pytest.raises(ValueError, match="wanted place"):
+        BatchBuilder(m, "cpu").build([StepEntry(a, [1], [1])])
+
+
+def test_fixed_capacity_batches_pad_onto_the_scratch_page():
+    m = manager([FULL], blocks=10, page=4, device="cpu")
+    a = m.open("a")
+    m.grow(a, 5); m.commit(a, 5); m.grow(a, 6)
+    capacity = BatchCapacity(4, 6)
+    buffer = torch.zeros(BatchBuilder.buffer_size(capacity, 1, (16,)), dtype=torch.int32)
+    batch = BatchBuilder(m, "cpu", (16,)).build([StepEntry(a, [3], [0])], capacity, buffer)
+    scratch = m.paged[0].scratch_page
+    assert batch.n_seqs == 4 and batch.real_seqs == 1 and batch.all_decode
+    assert batch.ctx_len.tolist() == [6, 1, 1, 1] and batch.positions.tolist() == [5, 0, 0, 0]
+    assert batch.groups[0].block_table.shape == (4, 6)
+    assert batch.groups[0].block_table[1].tolist() == [scratch] * 6
+    assert batch.groups[0].slot_map.tolist()[1:] == [scratch * 4] * 3
+    assert batch.state_slots.tolist()[1:] == [m.scratch_slot] * 3
+    assert batch.token_ids.data_ptr() == buffer.data_ptr()      # the descriptors sit at the fixed address
+    with pytest.raises(ValueError, match="one token per entry"):
+        BatchBuilder(m, "cpu").build([StepEntry(a, [3, 4], [0])], capacity, buffer)

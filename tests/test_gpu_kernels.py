@@ -1,0 +1,293 @@
+"""Each kernel alone against a plain 32-bit (or 64-bit) reference of the same operation, at sizes
+other than the engine's own tiny models: widths that are no power of two, head sizes in steps of
+16, any number of heads and groups, pages of several sizes."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import tolerance
+from plain_qwen3 import plain_attention, plain_rmsnorm, plain_rope_tables, plain_apply_rope, plain_sample
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from layover_b200 import ops as module
+    return module
+
+
+def close(got, expected, dtype, scale=1.0):
+    bound = tolerance(expected.float(), dtype) * scale
+    assert (got.float().cpu() - expected.float().cpu()).abs().max().item() <= bound
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab, hidden, tokens", [(50, 96, 7), (1000, 2560, 33), (3, 10, 1)])
+def test_embed(dtype, vocab, hidden, tokens):
+    table = torch.randn(vocab, hidden, device="cuda").to(dtype)
+    ids = torch.randint(0, vocab, (tokens,), device="cuda", dtype=torch.int32)
+    out = torch.empty(tokens, hidden, device="cuda", dtype=dtype)
+    ops().embed(ids, table, out)
+    assert torch.equal(out, table[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, hidden, eps", [(5, 96, 1e-5), (3, 2560, 1e-6), (2, 5000, 1e-6), (17, 16, 1e-3)])
+def test_add_rmsnorm(dtype, rows, hidden, eps):
+    x = torch.randn(rows, hidden, device="cuda").to(dtype)
+    delta = (0.5 * torch.randn(rows, hidden, device="cuda")).to(dtype)
+    weight = 1 + 0.2 * torch.randn(hidden, device="cuda")
+    summed = (x.float() + delta.float()).to(dtype)
+    expected = plain_rmsnorm(summed.cpu(), weight.cpu().to(dtype), eps)
+    x_run = x.clone()
+    out = torch.empty_like(x)
+    ops().add_rmsnorm(x_run, delta, weight.to(dtype).float(), eps, out)
+    assert torch.equal(x_run, summed)                                   # the residual stream holds the rounded sum
+    close(out, expected, dtype)
+    # without a delta, and for picked rows only (x untouched)
+    out2 = torch.empty_like(x)
+    ops().add_rmsnorm(x.clone(), None, weight.to(dtype).float(), eps, out2)
+    close(out2, plain_rmsnorm(x.cpu(), weight.cpu().to(dtype), eps), dtype)
+    picked = torch.tensor([rows - 1, 0], device="cuda", dtype=torch.int32)
+    x_keep = x.clone()
+    out3 = torch.empty(2, hidden, device="cuda", dtype=dtype)
+    ops().add_rmsnorm(x_keep, delta, weight.to(dtype).float(), eps, out3, picked)
+    assert torch.equal(x_keep, x)
+    close(out3, expected[[rows - 1, 0]], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m, n, k", [(1, 96, 64), (5, 200, 96), (64, 1000, 200), (130, 70, 2560), (3, 5, 7), (33, 257, 130)])
+def test_gemm_simt(dtype, m, n, k):
+    a = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(dtype)
+    expected = (a.double() @ w.double().T).float()
+    out = torch.empty(m, n, device="cuda", dtype=dtype)
+    ops().gemm_simt(a, w, out)
+    close(out, expected, dtype)
+    if dtype == torch.bfloat16:
+        wide = torch.empty(m, n, device="cuda", dtype=torch.float32)
+        ops().gemm_simt(a, w, wide)
+        close(wide, expected, torch.float32, scale=4)
+    # strided rows: a view into a wider matrix
+    big = torch.randn(m, k + 8, device="cuda").to(dtype)
+    out2 = torch.empty(m, n, device="cuda", dtype=dtype)
+    ops().gemm_simt(big[:, 4:4 + k], w, out2)
+    close(out2, (big[:, 4:4 + k].double() @ w.double().T).float(), dtype)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    a = torch.randn(70, 200, device="cuda")
+    w = torch.randn(96, 200, device="cuda")
+    full = torch.empty(70, 96, device="cuda")
+    ops().gemm_simt(a, w, full)
+    for lo, hi in ((0, 1), (63, 65), (5, 70)):
+        part = torch.empty(hi - lo, 96, device="cuda")
+        ops().gemm_simt(a[lo:hi].contiguous(), w, part)
+        assert torch.equal(part, full[lo:hi])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, inter", [(3, 200), (17, 9728), (1, 5)])
+def test_swiglu(dtype, tokens, inter):
+    gu = (2 * torch.randn(tokens, 2 * inter, device="cuda")).to(dtype)
+    out = torch.empty(tokens, inter, device="cuda", dtype=dtype)
+    ops().swiglu(gu, out)
+    expected = torch.nn.functional.silu(gu[:, :inter].cpu()) * gu[:, inter:].cpu()
+    close(out, expected, dtype)
+
+
+def paged_setup(dtype, lengths, kv_heads, dim, page, seed=0, poison=True):
+    """Random K and V for sequences of the given lengths, scattered over shuffled pages of a pool
+    whose unused slots hold NaN."""
+    gen = torch.Generator().manual_seed(seed)
+    pages_per = [-(-n // page) for n in lengths]
+    total = sum(pages_per) + 3
+    order = torch.randperm(total - 1, generator=gen).tolist()      # the last page stays unused (scratch)
+    fill = float("nan") if poison else 0.0
+    k_pool = torch.full((total, kv_heads, page, dim), fill, dtype=dtype)
+    v_pool = torch.full((total, kv_heads, page, dim), fill, dtype=dtype)
+    width = max(pages_per)
+    table = torch.full((len(lengths), width), total - 1, dtype=torch.int32)
+    ks, vs = [], []
+    for s, n in enumerate(lengths):
+        k = torch.randn(n, kv_heads, dim, generator=gen).to(dtype)
+        v = torch.randn(n, kv_heads, dim, generator=gen).to(dtype)
+        mine = [order.pop() for _ in range(pages_per[s])]
+        table[s, :len(mine)] = torch.tensor(mine, dtype=torch.int32)
+        for pos in range(n):
+            k_pool[mine[pos // page], :, pos % page] = k[pos]
+            v_pool[mine[pos // page], :, pos % page] = v[pos]
+        ks.append(k); vs.append(v)
+    return k_pool.cuda(), v_pool.cuda(), table.cuda(), ks, vs
+
+
+def run_attention(dtype, lengths, q_lens, q_heads, kv_heads, dim, page, window=0, seed=0, qs=None):
+    o = ops()
+    k_pool, v_pool, table, ks, vs = paged_setup(dtype, lengths, kv_heads, dim, page, seed)
+    gen = torch.Generator().manual_seed(seed + 1)
+    if qs is None:
+        qs = [torch.randn(n, q_heads, dim, generator=gen).to(dtype) for n in q_lens]
+    q = torch.cat(qs).reshape(-1, q_heads * dim).cuda()
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    bq = o.attention_simt_block_queries()
+    tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, bq)]
+    tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+    tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    o.attention_simt(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads, dim,
+                     page, 1.0 / math.sqrt(dim), window)
+    expected = []
+    for s, n in enumerate(lengths):
+        # the last q_lens[s] positions of a whole-sequence attention in which earlier queries are dummies
+        full_q = torch.zeros(n, q_heads, dim, dtype=dtype)
+        full_q[n - q_lens[s]:] = qs[s]
+        expected.append(plain_attention(full_q, ks[s], vs[s], window or None)[n - q_lens[s]:])
+    return out.cpu().view(-1, q_heads, dim), torch.cat(expected), ks, vs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads, kv_heads, dim, page", [(4, 2, 16, 4), (6, 1, 32, 16), (3, 3, 48, 8), (8, 2, 128, 16),
+                                                          (2, 1, 256, 16), (5, 5, 80, 2)])
+def test_attention_simt_mixed_segments(dtype, q_heads, kv_heads, dim, page):
+    # a whole prompt, a portion on top of history, single decoded tokens at page edges
+    lengths = [37, 100, page, page + 1, 2 * page - 1, 1, 65]
+    q_lens = [37, 9, 1, 1, 1, 1, 2]
+    got, expected, _, _ = run_attention(dtype, lengths, q_lens, q_heads, kv_heads, dim, page)
+    assert not torch.isnan(got).any()                  # NaN in unused slots and pages did not leak
+    close(got, expected, dtype)
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 33])
+def test_attention_simt_window_edges(window):
+    lengths, q_lens = [70, 40, 33], [70, 3, 1]
+    got, expected, _, _ = run_attention(torch.float32, lengths, q_lens, 4, 2, 32, 8, window=window)
+    close(got, expected, torch.float32)
+
+
+@pytest.mark.parametrize("far_key", [0, 15, 16, 17, 255, 256, 499, 500, 511])
+def test_attention_finds_one_far_key_among_hundreds(far_key):
+    """Random keys all look alike to a random query; here one key is made to stand out, so that a
+    kernel that skips or misplaces it (a page's edge, the first or last key) gives a different answer."""
+    dim, n = 64, 512
+    dtype = torch.float32
+    gen = torch.Generator().manual_seed(3)
+    direction = torch.randn(dim, generator=gen)
+    direction /= direction.norm()
+    q = (direction * 40.0).view(1, 1, dim)
+    k_pool, v_pool, table, ks, vs = paged_setup(dtype, [n], 1, dim, 16, seed=4)
+    page = int(table[0, far_key // 16])
+    k_pool[page, 0, far_key % 16] = (direction * 40.0).cuda()
+    marker = torch.full((dim,), 7.0)
+    v_pool[page, 0, far_key % 16] = marker.cuda()
+    o = ops()
+    out = torch.empty(1, dim, device="cuda")
+    one = torch.ones(1, dtype=torch.int32, device="cuda")
+    o.attention_simt(q.view(1, dim).cuda(), k_pool, v_pool, out, table, torch.tensor([0, 1], dtype=torch.int32, device="cuda"),
+                     n * one, 0 * one, 0 * one, 1, 1, 1, dim, 16, 1.0 / math.sqrt(dim))
+    assert (out.cpu() - marker).abs().max() < 1e-3     # score 200 against |scores| of a few: all weight on that key
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads, kv_heads, dim, page", [(4, 2, 16, 4), (6, 1, 32, 16), (32, 8, 128, 16), (2, 2, 256, 8),
+                                                          (3, 1, 80, 16)])
+def test_qk_norm_rope_kv(dtype, q_heads, kv_heads, dim, page):
+    o = ops()
+    tokens, eps, theta = 11, 1e-5, 50000.0
+    gen = torch.Generator().manual_seed(dim)
+    qkv = torch.randn(tokens, (q_heads + 2 * kv_heads) * dim, generator=gen).to(dtype)
+    qn = (1 + 0.2 * torch.randn(dim, generator=gen)).to(dtype)
+    kn = (1 + 0.2 * torch.randn(dim, generator=gen)).to(dtype)
+    positions = torch.tensor([0, 1, 2, 3, 500, 501, 7, 8, 9, 4000, 39999], dtype=torch.int32)
+    pages = 6
+    slots = torch.randperm(pages * page, generator=gen)[:tokens].to(torch.int32)
+    k_pool = torch.zeros(pages, kv_heads, page, dim, dtype=dtype, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(tokens, q_heads * dim, dtype=dtype, device="cuda")
+    inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).cuda()
+    o.qk_norm_rope_kv(qkv.cuda(), q_out, k_pool, v_pool, qn.float().cuda(), kn.float().cuda(), inv_freq,
+                      positions.cuda(), slots.cuda(), q_heads, kv_heads, dim, page, eps)
+    heads = qkv.view(tokens, q_heads + 2 * kv_heads, dim)
+    cos, sin = plain_rope_tables(positions, dim, theta, dtype)
+    q_ref = plain_apply_rope(plain_rmsnorm(heads[:, :q_heads], qn, eps), cos, sin)
+    k_ref = plain_apply_rope(plain_rmsnorm(heads[:, q_heads:q_heads + kv_heads], kn, eps), cos, sin)
+    v_ref = heads[:, q_heads + kv_heads:]
+    # positions up to 4e4 turn a rounding of the 32-bit angle into ~1e-3 of the cosine: compare loosely there
+    close(q_out.view(tokens, q_heads, dim), q_ref, dtype, scale=1.0 if dtype == torch.bfloat16 else 40.0)
+    for t in range(tokens):
+        pg, sl = int(slots[t]) // page, int(slots[t]) % page
+        close(k_pool[pg, :, sl], k_ref[t], dtype, scale=1.0 if dtype == torch.bfloat16 else 40.0)
+        assert torch.equal(v_pool[pg, :, sl].cpu(), v_ref[t])
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    written[slots.long()] = True
+    untouched = k_pool.permute(0, 2, 1, 3).reshape(pages * page, -1)[~written.cuda()]
+    assert float(untouched.abs().sum()) == 0.0          # nothing outside the given slots was written
+
+
+def test_qk_norm_rope_small_positions_are_tight():
+    o = ops()
+    dim, theta = 64, 10000.0
+    x = torch.randn(4, 3 * dim)
+    positions = torch.tensor([0, 1, 5, 17], dtype=torch.int32)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).cuda()
+    q_out = torch.empty(4, dim, device="cuda")
+    k_pool = torch.zeros(1, 1, 4, dim, device="cuda"); v_pool = torch.zeros_like(k_pool)
+    o.qk_norm_rope_kv(x.cuda(), q_out, k_pool, v_pool, None, None, inv_freq, positions.cuda(),
+                      torch.arange(4, dtype=torch.int32, device="cuda"), 1, 1, dim, 4, 0.0)
+    cos, sin = plain_rope_tables(positions, dim, theta, torch.float32)
+    expected = plain_apply_rope(x.view(4, 3, dim)[:, :1], cos, sin)
+    assert (q_out.cpu().view(4, 1, dim) - expected).abs().max() < 2e-6
+
+
+def test_refused_sizes_raise_instead_of_computing():
+    o = ops()
+    x = torch.zeros(2, 3 * 258, device="cuda")
+    with pytest.raises(ValueError, match="unsupported size"):
+        o.qk_norm_rope_kv(x, torch.zeros(2, 258, device="cuda"), None, None, None, None, None,
+                          torch.zeros(2, dtype=torch.int32, device="cuda"), None, 1, 1, 258, 4, 0.0)
+    with pytest.raises(ValueError, match="contiguous"):
+        o.swiglu(torch.zeros(4, 8, device="cuda").t(), torch.zeros(8, 2, device="cuda"))
+    with pytest.raises(Exception, match="CUDA"):
+        o.embed(torch.zeros(2, dtype=torch.int32), torch.zeros(3, 4), torch.zeros(2, 4))
+
+
+@pytest.mark.parametrize("vocab", [7, 512, 151936, 1000])
+def test_sampling_matches_the_plain_rule(vocab):
+    o = ops()
+    rows = 6
+    gen = torch.Generator().manual_seed(vocab)
+    logits = torch.randn(rows, vocab, generator=gen) * 3
+    logits[0, vocab // 2] = logits[0].max() + 1          # a clear maximum
+    logits[1, 3] = logits[1, 5] = logits[1].max() + 2    # equal maxima: the first wins
+    temperature = torch.tensor([0.0, 0.0, 0.8, 1.5, 0.8, 0.3])
+    seeds = [0, 0, 1234, 0xFFFFFFFF12345678, 1234, 99]
+    steps = [0, 0, 0, 7, 1, 4000000000]
+    lo = torch.tensor([s & 0xFFFFFFFF for s in seeds], dtype=torch.int64).to(torch.int32)
+    hi = torch.tensor([(s >> 32) & 0xFFFFFFFF for s in seeds], dtype=torch.int64).to(torch.int32)
+    st = torch.tensor(steps, dtype=torch.int64).to(torch.int32)
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    o.sample(logits.cuda(), temperature.cuda(), lo.cuda(), hi.cuda(), st.cuda(), tokens)
+    expected = [plain_sample(logits[r].numpy(), float(temperature[r]), seeds[r], steps[r]) for r in range(rows)]
+    assert tokens.tolist() == expected
+    assert expected[0] == vocab // 2 and expected[1] == 3
+    greedy = torch.empty(rows, dtype=torch.int32, device="cuda")
+    o.sample(logits.cuda(), None, None, None, None, greedy)
+    assert greedy.tolist() == logits.argmax(-1).tolist()
+
+
+def test_sampling_follows_the_distribution():
+    o = ops()
+    probs = torch.tensor([0.5, 0.25, 0.125, 0.125])
+    n = 4000
+    logits = probs.log().repeat(n, 1).cuda()
+    tokens = torch.empty(n, dtype=torch.int32, device="cuda")
+    zeros = torch.zeros(n, dtype=torch.int32, device="cuda")
+    o.sample(logits, torch.ones(n, device="cuda"), zeros + 77, zeros, torch.arange(n, dtype=torch.int32, device="cuda"), tokens)
+    freq = torch.bincount(tokens.long().cpu(), minlength=4).float() / n
+    assert (freq - probs).abs().max() < 0.03
