@@ -42,9 +42,12 @@ class _DecodeGraph:
             for _ in range(2):
                 step.model.forward(batch, step.cache)
         torch.cuda.current_stream().wait_stream(side)
+        from .. import ops
         self.graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
         with torch.cuda.graph(self.graph, pool=pool):
             self.logits = step.model.forward(batch, step.cache)
+        self.launches = ops.LAUNCHES - before      # kernels one replay runs
         return self.graph.pool()
 
 
@@ -64,6 +67,7 @@ class StepFunction:
         self._graph_pool = None
         self.steps = 0
         self.graph_replays = 0
+        self.replayed_launches = 0
 
     # ---- checks the kernels cannot make
     def _check(self, entries: list[StepEntry]) -> None:
@@ -111,6 +115,7 @@ class StepFunction:
                 batch = self.builder.build(entries, graph.capacity, graph.buffer)
                 graph.graph.replay()
                 self.graph_replays += 1
+                self.replayed_launches += graph.launches
                 rows = [i for i, e in enumerate(entries) if e.want]
                 logits = graph.logits[: len(entries)] if len(rows) == len(entries) else graph.logits[rows]
             else:

@@ -31,8 +31,13 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise ValueError(f"unsupported dtype {dtype}; the engine runs float32 or bfloat16") from None
 
 
+LAUNCHES = 0   # kernels of this package launched (or captured into a graph) so far
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code in _REFUSALS:
         raise ValueError(f"{what}: {_REFUSALS[code]}")
