@@ -30,7 +30,7 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "gemm_simt": ("gemm_simt.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
     "sampling": ("sampling.cu", ()),
-    "gemm_tcgen05": ("gemm_tcgen05.cu", ("-lcuda",)),
+    "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),
 }
 

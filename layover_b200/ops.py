@@ -213,11 +213,63 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None, seed_lo: torc
 
 
 # ------------------------------------------------------------------ the bfloat16 path
-BF16_LIBRARIES = ("elementwise", "gemm_simt", "attention_simt", "sampling")
+BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_simt", "sampling")
+
+_SCRATCH_FLOATS = 4 << 20     # split-K partial tiles (16 MiB)
+_SCRATCH_COUNTERS = 4096
+_scratch: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = {}
+
+
+def gemm_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """Per device: the split-K scratch, its tile counters (zero between launches) and the SM count.
+    Made once, outside any graph capture (models call this when their runtime is made)."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    if index not in _scratch:
+        with torch.cuda.device(index):
+            partials = torch.empty(_SCRATCH_FLOATS, dtype=torch.float32, device="cuda")
+            counters = torch.zeros(_SCRATCH_COUNTERS, dtype=torch.int32, device="cuda")
+        _scratch[index] = (partials, counters, torch.cuda.get_device_properties(index).multi_processor_count)
+    return _scratch[index]
+
+
+def gemm_tcgen05_supports(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """TMA needs 16-byte aligned bases and row strides: K-contiguous rows whose stride is a multiple of 8."""
+    return (a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores; bfloat16 in, out bfloat16 or float32."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        raise ValueError("gemm_tcgen05: operands must be 2-D bfloat16")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    partials, counters, sms = gemm_scratch(a.device)
+    fn = _fn("gemm_tcgen05", "lb_gemm_tcgen05",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_void_p, c_long,
+              c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
+              _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), sms, _stream()), "gemm_tcgen05")
+    return out
+
+
+def gemm_status() -> int:
+    """0, or the code a tensor-core product recorded when one of its bounded waits ran out
+    (1 loads, 2 MMAs, 3 epilogue). Synchronises; clears the code."""
+    lib = build.load("gemm_tcgen05")
+    lib.lb_gemm_tcgen05_status.restype = c_int
+    torch.cuda.synchronize()
+    return lib.lb_gemm_tcgen05_status()
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] = a[M, K] @ w[N, K]^T, bfloat16 operands, 32-bit accumulation; out bfloat16 or float32."""
+    """out[M, N] = a[M, K] @ w[N, K]^T, bfloat16 operands, 32-bit accumulation; out bfloat16 or float32.
+    Shapes that TMA cannot address (a row stride that is no multiple of 16 bytes) take the FFMA kernel."""
+    if gemm_tcgen05_supports(a, w):
+        return gemm_tcgen05(a, w, out)
     return gemm_simt(a, w, out)
 
 

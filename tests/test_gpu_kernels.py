@@ -291,3 +291,42 @@ def test_sampling_follows_the_distribution():
     o.sample(logits, torch.ones(n, device="cuda"), zeros + 77, zeros, torch.arange(n, dtype=torch.int32, device="cuda"), tokens)
     freq = torch.bincount(tokens.long().cpu(), minlength=4).float() / n
     assert (freq - probs).abs().max() < 0.03
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m, n, k", [
+    (1, 96, 64), (8, 2560, 4096), (16, 6144, 2560), (17, 200, 96), (33, 1000, 200), (64, 2560, 9728), (100, 392, 136),
+    (128, 256, 64), (129, 96, 64), (300, 200, 96), (2048, 640, 2560), (257, 1000, 264), (5, 8, 8), (8, 151936, 64),
+])
+def test_gemm_tcgen05(out_dtype, m, n, k):
+    o = ops()
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
+    expected = (a.double() @ w.double().T).float()
+    assert o.gemm_tcgen05_supports(a, w)
+    for _ in range(2):                                   # twice: a split-K tile counter must be back at zero
+        out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+        o.gemm_tcgen05(a, w, out)
+        assert o.gemm_status() == 0
+        assert not torch.isnan(out).any()
+        close(out, expected, out_dtype if out_dtype == torch.bfloat16 else torch.float32, scale=1.0 if out_dtype == torch.bfloat16 else 8.0)
+
+
+def test_gemm_tcgen05_strided_views_and_fallback():
+    o = ops()
+    big = torch.randn(40, 512, device="cuda").to(torch.bfloat16)
+    w = torch.randn(72, 128, device="cuda").to(torch.bfloat16) / 11
+    view = big[:, 128:256]                               # rows 1024 bytes apart, start 256 bytes in
+    out = torch.empty(40, 72, device="cuda", dtype=torch.bfloat16)
+    o.gemm_bf16(view, w, out)
+    close(out, (view.double() @ w.double().T).float(), torch.bfloat16)
+    wide = torch.empty(40, 80, device="cuda", dtype=torch.bfloat16)
+    o.gemm_bf16(view, w, wide[:, 3:75])                  # an output view that no vector store may touch
+    close(wide[:, 3:75], (view.double() @ w.double().T).float(), torch.bfloat16)
+    odd = torch.randn(9, 100, device="cuda").to(torch.bfloat16)[:, :99]   # K = 99: TMA cannot address it
+    w_odd = torch.randn(20, 99, device="cuda").to(torch.bfloat16)
+    assert not o.gemm_tcgen05_supports(odd, w_odd)
+    out = torch.empty(9, 20, device="cuda", dtype=torch.bfloat16)
+    o.gemm_bf16(odd, w_odd, out)
+    close(out, (odd.double() @ w_odd.double().T).float(), torch.bfloat16)
+    assert o.gemm_status() == 0
