@@ -1,0 +1,524 @@
+// Paged grouped-query attention for bfloat16 on tensor cores (mma.sync m16n8k16, 32-bit
+// accumulation, 32-bit softmax), read straight from the block table. The reference gathers the
+// history out of its pool and calls a library kernel for prompts (layover/model.py:84-90) and runs
+// one program per (sequence, query head) without splitting for decode
+// (layover/kernels/triton_decode.py:39-119, which re-reads each KV head once per query head).
+//
+// Two kernels share the tile code:
+//   prefill  one block per (tile of 64 queries of one sequence, query head); its four warps own 16
+//            query rows each and walk the keys in tiles of 64 with a two-stage cp.async pipeline;
+//            the causal mask (and a window) is applied from absolute positions.
+//   decode   one block per (sequence with a single new token, KV head, split of the context); the
+//            query heads that share the KV head are the rows of one 16-row MMA tile, so every key
+//            and value is read once for the whole group; the four warps take 16 keys each of every
+//            64-key tile and are merged at the end. With more than one split each block writes
+//            (max, sum, unnormalised output) to scratch memory and the block that arrives last at
+//            the (sequence, KV head) counter merges the splits in order and resets the counter.
+//
+// Keys outside [first visible key, context length) are loaded as zeros and masked by replacing
+// their scores, so stale or non-finite page contents cannot reach a result. Head sizes are
+// multiples of 16 up to 256 (a runtime value under a compile-time bound of 128 or 256).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int BKEYS = 64;     // keys per tile
+constexpr int BQ = 64;        // queries per prefill block (16 per warp)
+constexpr int PAD = 8;        // bf16 of padding per shared-memory row: rows 16 bytes apart modulo 128
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// 16-byte async copy; bytes == 0 writes zeros instead of reading
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Copies keys [tile * 64, +64) of one KV head into shared memory rows of (dim + PAD) bf16; keys
+// outside [key_lo, key_hi) become zeros. Thread t serves key t / 2 and half of its 16-byte chunks.
+__device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pool,
+                                             const bf16* __restrict__ v_pool, const int* __restrict__ table,
+                                             int tile, int key_lo, int key_hi, int kv_heads, int kv_head, int dim,
+                                             int page_tokens) {
+  const int j = threadIdx.x >> 1, half = threadIdx.x & 1;
+  const int key = tile * BKEYS + j;
+  const bool live = key >= key_lo && key < key_hi;
+  size_t at = 0;
+  if (live) {
+    const size_t page = (size_t)table[key / page_tokens];
+    at = ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * dim;
+  }
+  const int chunks = dim >> 3, per = (chunks + 1) >> 1;
+  const int stride = dim + PAD;
+  for (int c = half * per; c < min(chunks, (half + 1) * per); ++c) {
+    cp_async16(k_s + j * stride + c * 8, k_pool + at + c * 8, live ? 16 : 0);
+    cp_async16(v_s + j * stride + c * 8, v_pool + at + c * 8, live ? 16 : 0);
+  }
+}
+
+// ------------------------------------------------------------------------------- prefill
+template <int MAX_DIM>
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                         bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
+                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
+                         const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads, int kv_heads,
+                         int dim, int page_tokens, float scale_log2, int window) {
+  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, NT_S = BKEYS / 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int stride = dim + PAD;
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
+  bf16* k_s = q_s + BQ * stride;            // [2][BKEYS][stride]
+  bf16* v_s = k_s + 2 * BKEYS * stride;
+
+  const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x], head = blockIdx.y;
+  const int kv_head = head / (q_heads / kv_heads);
+  const int row0 = cu_q[seq], q_len = cu_q[seq + 1] - row0, ctx = ctx_len[seq];
+  const int start = ctx - q_len;
+  const int n_q = min(BQ, q_len - q0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int* table = block_table + (size_t)seq * table_width;
+  const int dk = dim >> 4;
+
+  const int p_first = start + q0, p_last = p_first + n_q - 1;
+  const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
+
+  {  // the block's queries
+    const int chunks = dim >> 3;
+    for (int i = threadIdx.x; i < BQ * chunks; i += THREADS) {
+      const int r = i / chunks, c = i % chunks;
+      const bool live = r < n_q;
+      const bf16* src = q + ((size_t)(row0 + q0 + (live ? r : 0)) * q_heads + head) * dim + c * 8;
+      cp_async16(q_s + r * stride + c * 8, src, live ? 16 : 0);
+    }
+  }
+  load_kv_tile(k_s, v_s, k_pool, v_pool, table, tile_lo, key_lo, p_last + 1, kv_heads, kv_head, dim, page_tokens);
+  cp_async_commit();
+
+  uint32_t qf[KSTEPS][4];
+  float o[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int p_row[2] = {p_first + warp * 16 + g, p_first + warp * 16 + g + 8};   // rows past n_q compute harmlessly
+
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+    const int buf = (tile - tile_lo) & 1;
+    if (tile < tile_hi) {
+      load_kv_tile(k_s + (buf ^ 1) * BKEYS * stride, v_s + (buf ^ 1) * BKEYS * stride, k_pool, v_pool, table, tile + 1,
+                   key_lo, p_last + 1, kv_heads, kv_head, dim, page_tokens);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (tile == tile_lo) {
+#pragma unroll
+      for (int k = 0; k < KSTEPS; ++k)
+        if (k < dk) ldmatrix_x4(qf[k], q_s + (warp * 16 + (lane & 15)) * stride + k * 16 + (lane >> 4) * 8);
+    }
+    const bf16* kt = k_s + buf * BKEYS * stride;
+    const bf16* vt = v_s + buf * BKEYS * stride;
+
+    // a warp whose rows all lie before this tile has nothing to do in it
+    const bool warp_active = tile * BKEYS <= p_first + warp * 16 + 15;
+    if (warp_active) {
+      float s[NT_S][4];
+#pragma unroll
+      for (int n = 0; n < NT_S; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KSTEPS; ++k) {
+        if (k < dk) {
+#pragma unroll
+          for (int n2 = 0; n2 < NT_S / 2; ++n2) {
+            uint32_t b[4];
+            ldmatrix_x4(b, kt + (n2 * 16 + (lane >> 4) * 8 + (lane & 7)) * stride + k * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[2 * n2], qf[k], b[0], b[1]);
+            mma_bf16(s[2 * n2 + 1], qf[k], b[2], b[3]);
+          }
+        }
+      }
+      // mask from absolute positions, running maximum and sum per row (two rows per thread)
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < NT_S; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = tile * BKEYS + n * 8 + 2 * t + (e & 1);
+          const int p = p_row[e >> 1];
+          const bool seen = key <= p && (window <= 0 || p - key < window);
+          s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[n][e]);
+        }
+      }
+      float alpha[2], base[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float m_new = fmaxf(m_run[r], tile_max[r]);
+        base[r] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[r] = fast_exp2(m_run[r] - base[r]);      // exp2(-inf) = 0 on the first tile
+        m_run[r] = m_new;
+      }
+      float tile_sum[2] = {0.f, 0.f};
+      uint32_t pf[NT_S / 2][4];
+#pragma unroll
+      for (int n = 0; n < NT_S; ++n) {
+        const float p0 = fast_exp2(s[n][0] - base[0]), p1 = fast_exp2(s[n][1] - base[0]);
+        const float p2 = fast_exp2(s[n][2] - base[1]), p3 = fast_exp2(s[n][3] - base[1]);
+        tile_sum[0] += p0 + p1;
+        tile_sum[1] += p2 + p3;
+        pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + tile_sum[r];
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) {
+        o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < BKEYS / 16; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < NT_O / 2; ++n2) {
+          if (n2 < dk) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, vt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * stride + n2 * 16 + (lane >> 4) * 8);
+            mma_bf16(o[2 * n2], pf[kk], b[0], b[1]);
+            mma_bf16(o[2 * n2 + 1], pf[kk], b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();   // the buffer may be overwritten by the next iteration's prefetch
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + g + 8 * r;
+    if (row >= n_q) continue;
+    const float inv = 1.0f / l_run[r];
+    bf16* dst = out + ((size_t)(row0 + q0 + row) * q_heads + head) * dim;
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      if (n * 8 < dim)
+        *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- decode
+// Rows 0..group-1 of the 16-row tile are the query heads of one KV head (group <= 16).
+template <int MAX_DIM>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
+                        const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
+                        const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim, int page_tokens,
+                        float scale_log2, int window, int splits, float* __restrict__ partials,
+                        unsigned* __restrict__ counters) {
+  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, STAGES = 3;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int stride = dim + PAD;
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);          // [16][stride]
+  bf16* k_s = q_s + 16 * stride;                          // [STAGES][BKEYS][stride]
+  bf16* v_s = k_s + STAGES * BKEYS * stride;
+  __shared__ unsigned last_flag;
+
+  const int seq = seq_list ? seq_list[blockIdx.x] : blockIdx.x;
+  const int kv_head = blockIdx.y, split = blockIdx.z;
+  const int group = q_heads / kv_heads, head0 = kv_head * group;
+  const int row = cu_q[seq];                               // the sequence's single query row
+  const int ctx = ctx_len[seq], p = ctx - 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int* table = block_table + (size_t)seq * table_width;
+  const int dk = dim >> 4;
+
+  const int key_lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int first_tile = key_lo / BKEYS, n_tiles = p / BKEYS + 1 - first_tile;
+  const int per_split = (n_tiles + splits - 1) / splits;
+  const int tile_begin = first_tile + split * per_split;
+  const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
+
+  {
+    const int chunks = dim >> 3;
+    for (int i = threadIdx.x; i < 16 * chunks; i += THREADS) {
+      const int r = i / chunks, c = i % chunks;
+      const bool live = r < group;
+      const bf16* src = q + ((size_t)row * q_heads + head0 + (live ? r : 0)) * dim + c * 8;
+      cp_async16(q_s + r * stride + c * 8, src, live ? 16 : 0);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (tile_begin + s < tile_end)
+      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, table, tile_begin + s, key_lo, ctx,
+                   kv_heads, kv_head, dim, page_tokens);
+    cp_async_commit();
+  }
+
+  uint32_t qf[KSTEPS][4];
+  float o[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int i = tile - tile_begin, buf = i % STAGES;
+    if (tile + STAGES - 1 < tile_end) {
+      const int nb = (i + STAGES - 1) % STAGES;
+      load_kv_tile(k_s + nb * BKEYS * stride, v_s + nb * BKEYS * stride, k_pool, v_pool, table, tile + STAGES - 1, key_lo,
+                   ctx, kv_heads, kv_head, dim, page_tokens);
+    }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+    if (i == 0) {
+#pragma unroll
+      for (int k = 0; k < KSTEPS; ++k)
+        if (k < dk) ldmatrix_x4(qf[k], q_s + (lane & 15) * stride + k * 16 + (lane >> 4) * 8);
+    }
+    const bf16* kt = k_s + buf * BKEYS * stride + warp * 16 * stride;   // this warp's 16 keys of the tile
+    const bf16* vt = v_s + buf * BKEYS * stride + warp * 16 * stride;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int k = 0; k < KSTEPS; ++k) {
+      if (k < dk) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kt + ((lane >> 4) * 8 + (lane & 7)) * stride + k * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[0], qf[k], b[0], b[1]);
+        mma_bf16(s[1], qf[k], b[2], b[3]);
+      }
+    }
+    float tile_max = -INFINITY;   // every row has the same position, so one mask serves both rows
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = tile * BKEYS + warp * 16 + n * 8 + 2 * t + (e & 1);
+        const bool seen = key <= p && key >= key_lo;
+        s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
+      }
+    }
+    float row_max[2] = {fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])),
+                        fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]))};
+    float alpha[2], base[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 1));
+      row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 2));
+      const float m_new = fmaxf(m_run[r], row_max[r]);
+      base[r] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = fast_exp2(m_run[r] - base[r]);
+      m_run[r] = m_new;
+    }
+    (void)tile_max;
+    uint32_t pf[4];
+    float tile_sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const float p0 = fast_exp2(s[n][0] - base[0]), p1 = fast_exp2(s[n][1] - base[0]);
+      const float p2 = fast_exp2(s[n][2] - base[1]), p3 = fast_exp2(s[n][3] - base[1]);
+      tile_sum[0] += p0 + p1;
+      tile_sum[1] += p2 + p3;
+      pf[n * 2] = pack_bf16(p0, p1);
+      pf[n * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + tile_sum[r];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int n2 = 0; n2 < NT_O / 2; ++n2) {
+      if (n2 < dk) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vt + (((lane >> 3) & 1) * 8 + (lane & 7)) * stride + n2 * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * n2], pf, b[0], b[1]);
+        mma_bf16(o[2 * n2 + 1], pf, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+
+  // ---- merge the four warps through shared memory (the tile buffers are free now)
+  __syncthreads();
+  float* merge = reinterpret_cast<float*>(smem_raw);      // [WARPS][16][dim + 2]: output, then max, then sum
+  const int mstride = dim + 2;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float* dst = merge + ((size_t)warp * 16 + g + 8 * r) * mstride;
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      if (n * 8 < dim) { dst[n * 8 + 2 * t] = o[n][2 * r]; dst[n * 8 + 2 * t + 1] = o[n][2 * r + 1]; }
+    }
+    if (t == 0) { dst[dim] = m_run[r]; dst[dim + 1] = l_run[r]; }
+  }
+  __syncthreads();
+  const unsigned tile_id = blockIdx.x * gridDim.y + blockIdx.y;
+  float* my_partial = partials ? partials + ((size_t)tile_id * splits + split) * group * mstride : nullptr;
+  for (int i = threadIdx.x; i < group * dim; i += THREADS) {
+    const int r = i / dim, c = i % dim;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + r) * mstride + dim]);
+    const float base = m_all == -INFINITY ? 0.f : m_all;
+    float acc = 0.f, l_all = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float* src = merge + ((size_t)w * 16 + r) * mstride;
+      const float f = fast_exp2(src[dim] - base);
+      acc += src[c] * f;
+      l_all += src[dim + 1] * f;
+    }
+    if (splits == 1) {
+      out[((size_t)row * q_heads + head0 + r) * dim + c] = __float2bfloat16_rn(acc / l_all);
+    } else {
+      my_partial[r * mstride + c] = acc;
+      if (c == 0) { my_partial[r * mstride + dim] = m_all; my_partial[r * mstride + dim + 1] = l_all; }
+    }
+  }
+  if (splits == 1) return;
+
+  // ---- the block that arrives last merges the splits in order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_flag = atomicAdd(&counters[tile_id], 1u) == (unsigned)splits - 1 ? 1u : 0u;
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  const float* all = partials + (size_t)tile_id * splits * group * mstride;
+  for (int i = threadIdx.x; i < group * dim; i += THREADS) {
+    const int r = i / dim, c = i % dim;
+    float m_all = -INFINITY;
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, all[((size_t)s * group + r) * mstride + dim]);
+    const float base = m_all == -INFINITY ? 0.f : m_all;
+    float acc = 0.f, l_all = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* src = all + ((size_t)s * group + r) * mstride;
+      const float f = fast_exp2(src[dim] - base);
+      acc += src[c] * f;
+      l_all += src[dim + 1] * f;
+    }
+    out[((size_t)row * q_heads + head0 + r) * dim + c] = __float2bfloat16_rn(acc / l_all);
+  }
+  if (threadIdx.x == 0) counters[tile_id] = 0;
+}
+
+size_t prefill_smem(int dim) { return (size_t)(BQ + 4 * BKEYS) * (dim + PAD) * sizeof(bf16); }
+size_t decode_smem(int dim) {
+  const size_t tiles = (size_t)(16 + 2 * 3 * BKEYS) * (dim + PAD) * sizeof(bf16);
+  const size_t merge = (size_t)WARPS * 16 * (dim + 2) * sizeof(float);
+  return tiles > merge ? tiles : merge;
+}
+}  // namespace
+
+LB_EXPORT int lb_attention_mma_block_queries() { return BQ; }
+
+// Prompt portions (any number of queries per sequence), listed as tiles of 64 queries.
+LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                        const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
+                                        const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
+                                        int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
+  const size_t smem = prefill_smem(dim);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_tiles, q_heads);
+  if (dim <= 128) {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem(128)); set = true; }
+    attention_prefill_kernel<128><<<grid, THREADS, smem, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window);
+  } else {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(attention_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem(256)); set = true; }
+    attention_prefill_kernel<256><<<grid, THREADS, smem, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window);
+  }
+  return lb_last_error();
+}
+
+// Floats of scratch that `splits` splits of `n_seqs` sequences need.
+LB_EXPORT long lb_attention_decode_scratch(int n_seqs, int q_heads, int dim, int splits) {
+  return splits <= 1 ? 0 : (long)n_seqs * q_heads * splits * (dim + 2);
+}
+
+// Sequences with one new token each. `seq_list` (n_seqs indices into cu_q / ctx_len / block_table)
+// may be null for "all of them in order". `counters` (n_seqs * kv_heads, zero between launches) and
+// `partials` are needed when splits > 1.
+LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                       const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
+                                       const int* seq_list, int n_seqs, int q_heads, int kv_heads, int dim,
+                                       int page_tokens, float scale, int window, int splits, float* partials,
+                                       long partial_floats, unsigned* counters, int n_counters, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads / kv_heads > 16 ||
+      kv_heads > 65535 || splits < 1 || splits > 65535)
+    return LB_ERR_SIZE;
+  if (splits > 1 && (!partials || !counters || lb_attention_decode_scratch(n_seqs, q_heads, dim, splits) > partial_floats ||
+                     (long)n_seqs * kv_heads > n_counters))
+    return LB_ERR_SIZE;
+  const size_t smem = decode_smem(dim);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_seqs, kv_heads, splits);
+  if (dim <= 128) {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128)); set = true; }
+    attention_decode_kernel<128><<<grid, THREADS, smem, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
+        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters);
+  } else {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(256)); set = true; }
+    attention_decode_kernel<256><<<grid, THREADS, smem, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
+        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters);
+  }
+  return lb_last_error();
+}

@@ -40,6 +40,7 @@ def make_runtime(dtype: torch.dtype, device: torch.device | str) -> Runtime:
         runtime.kernel_libraries = ("elementwise", "gemm_simt", "attention_simt", "sampling")
     elif dtype == torch.bfloat16:
         ops.gemm_scratch(device)      # made now, never inside a graph capture
+        ops.attention_scratch(device)
         runtime = Runtime(dtype, device, _linear_bf16)
         runtime.attention = ops.attention_bf16
         runtime.tile_sizes = ops.attention_bf16_tile_sizes()

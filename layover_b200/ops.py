@@ -213,7 +213,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None, seed_lo: torc
 
 
 # ------------------------------------------------------------------ the bfloat16 path
-BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_simt", "sampling")
+BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_mma", "sampling")
 
 _SCRATCH_FLOATS = 4 << 20     # split-K partial tiles (16 MiB)
 _SCRATCH_COUNTERS = 4096
@@ -273,11 +273,88 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
     return gemm_simt(a, w, out)
 
 
+_attn_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+_ATTN_SCRATCH_FLOATS = 8 << 20     # split-K partial outputs (32 MiB)
+_ATTN_COUNTERS = 1 << 16
+
+
+def attention_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per device: scratch for the decode kernel's split partials and its (sequence, KV head) counters."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    if index not in _attn_scratch:
+        with torch.cuda.device(index):
+            _attn_scratch[index] = (torch.empty(_ATTN_SCRATCH_FLOATS, dtype=torch.float32, device="cuda"),
+                                    torch.zeros(_ATTN_COUNTERS, dtype=torch.int32, device="cuda"))
+    return _attn_scratch[index]
+
+
+def attention_mma_block_queries() -> int:
+    lib = build.load("attention_mma")
+    lib.lb_attention_mma_block_queries.restype = c_int
+    return lib.lb_attention_mma_block_queries()
+
+
+def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, tile_seq, tile_q0, n_tiles, q_heads,
+                           kv_heads, dim, page_tokens, scale, window=0):
+    """Tensor-core paged attention for prompt portions: tiles of 64 queries, any number of queries per sequence."""
+    for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len), ("tile_seq", tile_seq),
+                    ("tile_q0", tile_q0)):
+        _need(t, torch.int32, name)
+    fn = _fn("attention_mma", "lb_attention_prefill_bf16",
+             [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
+              _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads, kv_heads, dim, page_tokens, float(scale),
+              int(window), _stream()), "attention_prefill_bf16")
+    return out
+
+
+def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> int:
+    """How many ways to split the context so that about two blocks per SM are in flight."""
+    natural = n_seqs * kv_heads
+    splits = max(1, -(-2 * sm_count // natural))
+    splits = min(splits, max(1, -(-max_context // 256)))      # at least 256 keys per split
+    while splits > 1 and n_seqs * q_heads * splits * (dim + 2) > _ATTN_SCRATCH_FLOATS:
+        splits -= 1
+    return splits
+
+
+def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, seq_list, n_seqs, q_heads, kv_heads, dim,
+                          page_tokens, scale, window=0, splits=1):
+    """Tensor-core paged attention for sequences with one new token each, the context split `splits` ways."""
+    for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len)):
+        _need(t, torch.int32, name)
+    if seq_list is not None:
+        _need(seq_list, torch.int32, "seq_list")
+    partials, counters = attention_scratch(q.device)
+    fn = _fn("attention_mma", "lb_attention_decode_bf16",
+             [c_void_p] * 5 + [c_int] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p, c_long, c_void_p,
+                                                                        c_int, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
+              _ptr(ctx_len), _ptr(seq_list), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale), int(window),
+              int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), _stream()),
+           "attention_decode_bf16")
+    return out
+
+
 def attention_bf16_tile_sizes() -> tuple[int, ...]:
-    return (attention_simt_block_queries(),)
+    return (attention_mma_block_queries(),)
 
 
 def attention_bf16(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
-    tiles = batch.tiles[attention_simt_block_queries()]
-    attention_simt(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
-                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
+    """The bfloat16 path's attention for one step: the split decode kernel when every sequence brings a
+    single token, else the tile kernel over the step's query tiles."""
+    if batch.all_decode and q_heads // kv_heads <= 16:
+        sms = gemm_scratch(q.device)[2]
+        # the widest context the block table can describe (what a captured step may later see)
+        splits = decode_splits(batch.n_seqs, q_heads, kv_heads, dim, block_table.shape[1] * page_tokens, sms)
+        attention_decode_bf16(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, None, batch.n_seqs,
+                              q_heads, kv_heads, dim, page_tokens, scale, window, splits)
+        return
+    tiles = batch.tiles[attention_mma_block_queries()]
+    attention_prefill_bf16(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
+                           tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)

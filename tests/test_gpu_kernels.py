@@ -127,7 +127,8 @@ def paged_setup(dtype, lengths, kv_heads, dim, page, seed=0, poison=True):
     return k_pool.cuda(), v_pool.cuda(), table.cuda(), ks, vs
 
 
-def run_attention(dtype, lengths, q_lens, q_heads, kv_heads, dim, page, window=0, seed=0, qs=None):
+def run_attention(dtype, lengths, q_lens, q_heads, kv_heads, dim, page, window=0, seed=0, qs=None, kernel="simt",
+                  splits=1):
     o = ops()
     k_pool, v_pool, table, ks, vs = paged_setup(dtype, lengths, kv_heads, dim, page, seed)
     gen = torch.Generator().manual_seed(seed + 1)
@@ -136,13 +137,22 @@ def run_attention(dtype, lengths, q_lens, q_heads, kv_heads, dim, page, window=0
     q = torch.cat(qs).reshape(-1, q_heads * dim).cuda()
     cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device="cuda")
     ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
-    bq = o.attention_simt_block_queries()
+    bq = o.attention_simt_block_queries() if kernel == "simt" else o.attention_mma_block_queries()
     tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, bq)]
     tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
     tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
     out = torch.full_like(q, float("nan"))
-    o.attention_simt(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads, dim,
-                     page, 1.0 / math.sqrt(dim), window)
+    scale = 1.0 / math.sqrt(dim)
+    if kernel == "simt":
+        o.attention_simt(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads, dim,
+                         page, scale, window)
+    elif kernel == "prefill":
+        o.attention_prefill_bf16(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads,
+                                 kv_heads, dim, page, scale, window)
+    else:
+        assert all(n == 1 for n in q_lens)
+        o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, ctx, None, len(lengths), q_heads, kv_heads, dim,
+                                page, scale, window, splits)
     expected = []
     for s, n in enumerate(lengths):
         # the last q_lens[s] positions of a whole-sequence attention in which earlier queries are dummies
@@ -330,3 +340,61 @@ def test_gemm_tcgen05_strided_views_and_fallback():
     o.gemm_bf16(odd, w_odd, out)
     close(out, (odd.double() @ w_odd.double().T).float(), torch.bfloat16)
     assert o.gemm_status() == 0
+
+
+@pytest.mark.parametrize("q_heads, kv_heads, dim, page", [(4, 2, 16, 4), (6, 1, 32, 16), (3, 3, 48, 8), (32, 8, 128, 16),
+                                                          (2, 1, 256, 16), (5, 5, 80, 2), (16, 2, 64, 32), (8, 2, 144, 16)])
+def test_attention_prefill_bf16(q_heads, kv_heads, dim, page):
+    lengths = [37, 300, page, page + 1, 2 * page - 1, 1, 65, 64, 200]
+    q_lens = [37, 129, 1, 1, 1, 1, 2, 64, 70]
+    got, expected, _, _ = run_attention(torch.bfloat16, lengths, q_lens, q_heads, kv_heads, dim, page, kernel="prefill")
+    assert not torch.isnan(got).any()
+    close(got, expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_prefill_bf16_window(window):
+    got, expected, _, _ = run_attention(torch.bfloat16, [270, 140, 33], [270, 3, 1], 4, 2, 32, 8, window=window, kernel="prefill")
+    close(got, expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("q_heads, kv_heads, dim, page", [(4, 2, 16, 4), (6, 1, 32, 16), (32, 8, 128, 16), (2, 1, 256, 16),
+                                                          (16, 1, 64, 8), (5, 5, 80, 2)])
+def test_attention_decode_bf16(q_heads, kv_heads, dim, page, splits):
+    lengths = [1, 2, page, page + 1, 63, 64, 65, 127, 128, 129, 700, 1000, 257]
+    for _ in range(2):                                 # twice: the split counters must be back at zero
+        got, expected, _, _ = run_attention(torch.bfloat16, lengths, [1] * len(lengths), q_heads, kv_heads, dim, page,
+                                            kernel="decode", splits=splits)
+        assert not torch.isnan(got).any()
+        close(got, expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("window", [1, 7, 64, 65, 300])
+def test_attention_decode_bf16_window(window):
+    lengths = [1, 50, 64, 65, 300, 777]
+    got, expected, _, _ = run_attention(torch.bfloat16, lengths, [1] * 6, 4, 2, 32, 8, window=window, kernel="decode", splits=3)
+    close(got, expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("kernel", ["prefill", "decode"])
+@pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 65, 255, 256, 1023, 1024, 1500, 2046, 2047])
+def test_bf16_attention_finds_one_far_key_among_thousands(kernel, far_key):
+    dim, n = 128, 2048
+    gen = torch.Generator().manual_seed(3)
+    direction = torch.randn(dim, generator=gen)
+    direction /= direction.norm()
+    k_pool, v_pool, table, ks, vs = paged_setup(torch.bfloat16, [n], 1, dim, 16, seed=4)
+    page = int(table[0, far_key // 16])
+    k_pool[page, 0, far_key % 16] = (direction * 40.0).to(torch.bfloat16).cuda()
+    v_pool[page, 0, far_key % 16] = 7.0
+    o = ops()
+    q = (direction * 40.0).to(torch.bfloat16).view(1, dim).cuda()
+    out = torch.empty(1, dim, device="cuda", dtype=torch.bfloat16)
+    one = torch.ones(1, dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    if kernel == "prefill":
+        o.attention_prefill_bf16(q, k_pool, v_pool, out, table, cu, n * one, 0 * one, 0 * one, 1, 1, 1, dim, 16, 1.0 / math.sqrt(dim))
+    else:
+        o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, n * one, None, 1, 1, 1, dim, 16, 1.0 / math.sqrt(dim), 0, 7)
+    assert (out.float().cpu() - 7.0).abs().max() < 0.05
