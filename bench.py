@@ -231,6 +231,14 @@ def run_ours(args) -> dict:
     gen = torch.Generator().manual_seed(0)
     model = lb.random_model(cfg, seed=0, device="cuda", dtype=args.dtype, std=0.02)
     pk, pk_source = peaks()
+    if args.only == "decode":
+        point = decode_point(model, args.batch, args.steps, args.warmup, gen)
+        return {"only": "decode", "batch": args.batch, "layers_run": cfg.num_hidden_layers,
+                "tok_s": round(point["tok_s"], 1), "ms_per_step": round(point["ms_per_step"], 4)}
+    if args.only == "prefill":
+        point = prefill_point(model, gen, repeats=max(1, args.steps))
+        return {"only": "prefill", "layers_run": cfg.num_hidden_layers, "tok_s": round(point["tok_s"], 1),
+                "ms": round(point["ms"], 3)}
     clocks = ClockSampler()
     main = decode_point(model, args.batch, args.steps, args.warmup, gen, clocks)
     prefill = prefill_point(model, gen)
@@ -369,6 +377,8 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the shape has (both numbers are reported)")
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                        help="decode or prefill alone, as a small target for a profiler (prints a short line)")
     args = parser.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

@@ -62,25 +62,70 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Copies keys [tile * 64, +64) of one KV head into shared memory rows of (dim + PAD) bf16; keys
-// outside [key_lo, key_hi) become zeros. Thread t serves key t / 2 and half of its 16-byte chunks.
-__device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pool,
-                                             const bf16* __restrict__ v_pool, const int* __restrict__ table,
-                                             int tile, int key_lo, int key_hi, int kv_heads, int kv_head, int dim,
-                                             int page_tokens) {
-  const int j = threadIdx.x >> 1, half = threadIdx.x & 1;
-  const int key = tile * BKEYS + j;
-  const bool live = key >= key_lo && key < key_hi;
-  size_t at = 0;
-  if (live) {
-    const size_t page = (size_t)table[key / page_tokens];
-    at = ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * dim;
+constexpr int TABLE_CACHE = 1024;   // block-table entries a block keeps in shared memory
+
+// The pages of keys [first_key, last_key] copied to shared memory once, so that the tile loads do
+// not wait on a dependent global read each; entries past the cache are read from global memory.
+struct TableSlice {
+  const int* table;
+  const int* cached;
+  int first_page;
+  __device__ __forceinline__ int page(int index) const {
+    const int local = index - first_page;
+    return (local >= 0 && local < TABLE_CACHE) ? cached[local] : table[index];
   }
-  const int chunks = dim >> 3, per = (chunks + 1) >> 1;
-  const int stride = dim + PAD;
-  for (int c = half * per; c < min(chunks, (half + 1) * per); ++c) {
-    cp_async16(k_s + j * stride + c * 8, k_pool + at + c * 8, live ? 16 : 0);
-    cp_async16(v_s + j * stride + c * 8, v_pool + at + c * 8, live ? 16 : 0);
+};
+
+__device__ __forceinline__ TableSlice cache_table(int* cached, const int* __restrict__ table, int first_key,
+                                                   int last_key, int page_tokens) {
+  const int first_page = first_key / page_tokens, n = min(TABLE_CACHE, last_key / page_tokens - first_page + 1);
+  for (int i = threadIdx.x; i < n; i += THREADS) cached[i] = table[first_page + i];
+  return TableSlice{table, cached, first_page};
+}
+
+// Copies keys [tile * 64, +64) of one KV head into shared memory rows of (dim + PAD) bf16; keys
+// outside [key_lo, key_hi) become zeros. Consecutive threads take consecutive 16-byte pieces, and
+// a page of one head is one contiguous run, so every request is a full line.
+struct TileShape {
+  int kv_heads, kv_head, dim, page_tokens;
+  int chunk_shift;   // log2(dim / 8) when that is a power of two, else -1
+  int page_shift;    // log2(page_tokens) when that is a power of two, else -1
+};
+
+__device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pool,
+                                             const bf16* __restrict__ v_pool, const TableSlice& pages,
+                                             int tile, int key_lo, int key_hi, const TileShape& shape) {
+  const int dim = shape.dim, stride = dim + PAD, page_tokens = shape.page_tokens;
+  if (shape.chunk_shift >= 0 && shape.page_shift >= 0) {
+    // shifts and masks only: the thread's piece of a row and its first key are fixed for the kernel
+    const int c8 = (threadIdx.x & ((1 << shape.chunk_shift) - 1)) * 8;
+    const int keys_per_pass = THREADS >> shape.chunk_shift;
+#pragma unroll 4
+    for (int j = threadIdx.x >> shape.chunk_shift; j < BKEYS; j += keys_per_pass) {
+      const int key = tile * BKEYS + j;
+      const bool live = key >= key_lo && key < key_hi;
+      size_t at = 0;
+      if (live) {
+        const int index = key >> shape.page_shift;
+        at = (((size_t)pages.page(index) * shape.kv_heads + shape.kv_head) * page_tokens + (key & (page_tokens - 1))) * dim + c8;
+      }
+      cp_async16(k_s + j * stride + c8, k_pool + at, live ? 16 : 0);
+      cp_async16(v_s + j * stride + c8, v_pool + at, live ? 16 : 0);
+    }
+    return;
+  }
+  const int chunks = dim >> 3;
+  for (int i = threadIdx.x; i < BKEYS * chunks; i += THREADS) {
+    const int j = i / chunks, c = i - j * chunks;
+    const int key = tile * BKEYS + j;
+    const bool live = key >= key_lo && key < key_hi;
+    size_t at = 0;
+    if (live) {
+      const int index = key / page_tokens;
+      at = (((size_t)pages.page(index) * shape.kv_heads + shape.kv_head) * page_tokens + (key - index * page_tokens)) * dim + c * 8;
+    }
+    cp_async16(k_s + j * stride + c * 8, k_pool + at, live ? 16 : 0);
+    cp_async16(v_s + j * stride + c * 8, v_pool + at, live ? 16 : 0);
   }
 }
 
@@ -91,13 +136,16 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads, int kv_heads,
-                         int dim, int page_tokens, float scale_log2, int window) {
+                         int dim, int page_tokens, float scale_log2, int window, int chunk_shift, int page_shift) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, NT_S = BKEYS / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int stride = dim + PAD;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
   bf16* k_s = q_s + BQ * stride;            // [2][BKEYS][stride]
   bf16* v_s = k_s + 2 * BKEYS * stride;
+  __shared__ int table_cache[TABLE_CACHE];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x], head = blockIdx.y;
   const int kv_head = head / (q_heads / kv_heads);
@@ -111,6 +159,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   const int p_first = start + q0, p_last = p_first + n_q - 1;
   const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
+  const TableSlice pages = cache_table(table_cache, table, key_lo, p_last, page_tokens);
+  const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
+  __syncthreads();
 
   {  // the block's queries
     const int chunks = dim >> 3;
@@ -121,7 +172,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       cp_async16(q_s + r * stride + c * 8, src, live ? 16 : 0);
     }
   }
-  load_kv_tile(k_s, v_s, k_pool, v_pool, table, tile_lo, key_lo, p_last + 1, kv_heads, kv_head, dim, page_tokens);
+  load_kv_tile(k_s, v_s, k_pool, v_pool, pages, tile_lo, key_lo, p_last + 1, shape);
   cp_async_commit();
 
   uint32_t qf[KSTEPS][4];
@@ -134,8 +185,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int buf = (tile - tile_lo) & 1;
     if (tile < tile_hi) {
-      load_kv_tile(k_s + (buf ^ 1) * BKEYS * stride, v_s + (buf ^ 1) * BKEYS * stride, k_pool, v_pool, table, tile + 1,
-                   key_lo, p_last + 1, kv_heads, kv_head, dim, page_tokens);
+      load_kv_tile(k_s + (buf ^ 1) * BKEYS * stride, v_s + (buf ^ 1) * BKEYS * stride, k_pool, v_pool, pages, tile + 1,
+                   key_lo, p_last + 1, shape);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -252,7 +303,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                         const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim, int page_tokens,
                         float scale_log2, int window, int splits, float* __restrict__ partials,
-                        unsigned* __restrict__ counters) {
+                        unsigned* __restrict__ counters, int chunk_shift, int page_shift) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, STAGES = 3;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int stride = dim + PAD;
@@ -260,6 +311,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   bf16* k_s = q_s + 16 * stride;                          // [STAGES][BKEYS][stride]
   bf16* v_s = k_s + STAGES * BKEYS * stride;
   __shared__ unsigned last_flag;
+  __shared__ int table_cache[TABLE_CACHE];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int seq = seq_list ? seq_list[blockIdx.x] : blockIdx.x;
   const int kv_head = blockIdx.y, split = blockIdx.z;
@@ -275,6 +329,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const int per_split = (n_tiles + splits - 1) / splits;
   const int tile_begin = first_tile + split * per_split;
   const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
+  const TableSlice pages = cache_table(table_cache, table, max(key_lo, tile_begin * BKEYS),
+                                       min(p, max(tile_end, tile_begin + 1) * BKEYS - 1), page_tokens);
+  const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
+  __syncthreads();
 
   {
     const int chunks = dim >> 3;
@@ -288,8 +346,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (tile_begin + s < tile_end)
-      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, table, tile_begin + s, key_lo, ctx,
-                   kv_heads, kv_head, dim, page_tokens);
+      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_begin + s, key_lo, ctx,
+                   shape);
     cp_async_commit();
   }
 
@@ -303,8 +361,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const int i = tile - tile_begin, buf = i % STAGES;
     if (tile + STAGES - 1 < tile_end) {
       const int nb = (i + STAGES - 1) % STAGES;
-      load_kv_tile(k_s + nb * BKEYS * stride, v_s + nb * BKEYS * stride, k_pool, v_pool, table, tile + STAGES - 1, key_lo,
-                   ctx, kv_heads, kv_head, dim, page_tokens);
+      load_kv_tile(k_s + nb * BKEYS * stride, v_s + nb * BKEYS * stride, k_pool, v_pool, pages, tile + STAGES - 1, key_lo,
+                   ctx, shape);
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
@@ -431,23 +489,47 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   if (!last_flag) return;
   __threadfence();
   const float* all = partials + (size_t)tile_id * splits * group * mstride;
+  // per (split, row): the factor that brings the split's sums to the common maximum, in shared
+  // memory first, so that the loads of the second pass do not wait on one another
+  float* factor = merge;                                   // [splits][group], then [group] sums
+  float* l_total = merge + (size_t)splits * group;
+  __syncthreads();
+  float* m_part = l_total + group;                         // [splits][group] maxima, then sums
+  float* l_part = m_part + (size_t)splits * group;
+  for (int i = threadIdx.x; i < splits * group; i += THREADS) {   // every (split, row) is its own load
+    const float* src = all + (size_t)i * mstride;
+    m_part[i] = src[dim];
+    l_part[i] = src[dim + 1];
+  }
+  __syncthreads();
+  for (int r = threadIdx.x; r < group; r += THREADS) {
+    float m_all = -INFINITY;
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, m_part[s * group + r]);
+    const float base = m_all == -INFINITY ? 0.f : m_all;
+    float l_all = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float f = fast_exp2(m_part[s * group + r] - base);
+      factor[s * group + r] = f;
+      l_all += l_part[s * group + r] * f;
+    }
+    l_total[r] = l_all;
+  }
+  __syncthreads();
   for (int i = threadIdx.x; i < group * dim; i += THREADS) {
     const int r = i / dim, c = i % dim;
-    float m_all = -INFINITY;
-    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, all[((size_t)s * group + r) * mstride + dim]);
-    const float base = m_all == -INFINITY ? 0.f : m_all;
-    float acc = 0.f, l_all = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* src = all + ((size_t)s * group + r) * mstride;
-      const float f = fast_exp2(src[dim] - base);
-      acc += src[c] * f;
-      l_all += src[dim + 1] * f;
-    }
-    out[((size_t)row * q_heads + head0 + r) * dim + c] = __float2bfloat16_rn(acc / l_all);
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) acc += all[((size_t)s * group + r) * mstride + c] * factor[s * group + r];
+    out[((size_t)row * q_heads + head0 + r) * dim + c] = __float2bfloat16_rn(acc / l_total[r]);
   }
   if (threadIdx.x == 0) counters[tile_id] = 0;
 }
 
+int exact_log2(int v) {
+  int shift = 0;
+  while ((1 << shift) < v) ++shift;
+  return (1 << shift) == v ? shift : -1;
+}
 size_t prefill_smem(int dim) { return (size_t)(BQ + 4 * BKEYS) * (dim + PAD) * sizeof(bf16); }
 size_t decode_smem(int dim) {
   const size_t tiles = (size_t)(16 + 2 * 3 * BKEYS) * (dim + PAD) * sizeof(bf16);
@@ -467,19 +549,20 @@ LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
   const size_t smem = prefill_smem(dim);
   const float scale_log2 = scale * 1.4426950408889634f;
+  const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_tiles, q_heads);
   if (dim <= 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem(128)); set = true; }
-    attention_prefill_kernel<128><<<grid, THREADS, smem, stream>>>(
+    lb_launch(attention_prefill_kernel<128>, grid, THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window);
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(attention_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem(256)); set = true; }
-    attention_prefill_kernel<256><<<grid, THREADS, smem, stream>>>(
+    lb_launch(attention_prefill_kernel<256>, grid, THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window);
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift);
   }
   return lb_last_error();
 }
@@ -505,20 +588,24 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
                      (long)n_seqs * kv_heads > n_counters))
     return LB_ERR_SIZE;
   const size_t smem = decode_smem(dim);
+  if ((3 * (size_t)splits + 1) * (q_heads / kv_heads) * sizeof(float) > smem) return LB_ERR_SIZE;   // merge factors
   const float scale_log2 = scale * 1.4426950408889634f;
+  const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_seqs, kv_heads, splits);
   if (dim <= 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128)); set = true; }
-    attention_decode_kernel<128><<<grid, THREADS, smem, stream>>>(
+    lb_launch(attention_decode_kernel<128>, grid, THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters);
+        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
+        page_shift);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(256)); set = true; }
-    attention_decode_kernel<256><<<grid, THREADS, smem, stream>>>(
+    lb_launch(attention_decode_kernel<256>, grid, THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters);
+        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
+        page_shift);
   }
   return lb_last_error();
 }

@@ -35,6 +35,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads,
                             int kv_heads, int dim, int page_tokens, float scale, int window) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   float* q_s = smem;                               // [BQ][dim]
   float* k_s = q_s + BQ * dim;                     // [BKEYS][dim + 1]
   float* v_s = k_s + BKEYS * (dim + 1);            // [BKEYS][dim]
@@ -139,13 +141,13 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
   if (dtype == LB_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    paged_attention_simt_kernel<float><<<grid, WARPS * 32, smem, stream>>>(
+    lb_launch(paged_attention_simt_kernel<float>, grid, WARPS * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table, table_width, cu_q,
         ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window);
   } else if (dtype == LB_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    paged_attention_simt_kernel<bf16><<<grid, WARPS * 32, smem, stream>>>(
+    lb_launch(paged_attention_simt_kernel<bf16>, grid, WARPS * 32, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
         tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window);
   } else

@@ -62,3 +62,38 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 static inline int lb_last_error() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch
+// Every kernel of this package is launched so that it may start while its predecessor in the
+// stream is still running: its blocks set themselves up (and a matrix product already streams
+// weights, which no kernel writes) and then wait in `pdl_wait()` until the predecessor has
+// finished and its writes are visible. Every kernel calls `pdl_wait()` before it touches memory
+// that an earlier kernel wrote or that a later kernel may still read, so completion is
+// transitive along the stream. LAYOVER_B200_PDL=0 launches the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool lb_pdl_enabled() {
+  static const bool enabled = [] {
+    const char* v = std::getenv("LAYOVER_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int lb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = lb_pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}

@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ x,
                              int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   const T* src = table + (size_t)ids[blockIdx.x] * hidden;
   T* dst = x + (size_t)blockIdx.x * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
@@ -18,9 +20,9 @@ LB_EXPORT int lb_embed(int dtype, const int* ids, const void* table, void* x, in
                        cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dtype == LB_F32)
-    embed_kernel<float><<<tokens, 256, 0, stream>>>(ids, (const float*)table, (float*)x, hidden);
+    lb_launch(embed_kernel<float>, tokens, 256, 0, stream, ids, (const float*)table, (float*)x, hidden);
   else if (dtype == LB_BF16)
-    embed_kernel<bf16><<<tokens, 256, 0, stream>>>(ids, (const bf16*)table, (bf16*)x, hidden);
+    lb_launch(embed_kernel<bf16>, tokens, 256, 0, stream, ids, (const bf16*)table, (bf16*)x, hidden);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();
@@ -31,29 +33,117 @@ LB_EXPORT int lb_embed(int dtype, const int* ids, const void* table, void* x, in
 // picked), out = weight * round_T(v * rsqrt(mean(v^2) + eps))   (layover/model.py:31-36,165-166)
 // With `rows`, output row r reads source row rows[r] and x is not written (final norm of the
 // wanted rows only). The norm weight is always 32-bit.
-template <typename T>
+// eight (bf16) or four (float) elements per 16-byte access
+template <typename T> struct Pack;
+template <> struct Pack<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Pack<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+      v[2 * i] = __low2float(pair);
+      v[2 * i + 1] = __high2float(pair);
+    }
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <typename T, bool VEC>
 __global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
                                    T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
   extern __shared__ float row_vals[];  // hidden floats + 33 for the reduction
+  pdl_launch_dependents();
+  pdl_wait();
   float* scratch = row_vals + hidden;
   const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
   T* xr = x + src * hidden;
   const T* dr = delta ? delta + src * hidden : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = Elem<T>::load(xr + i);
-    if (dr) {
-      v = Elem<T>::round(v + Elem<T>::load(dr + i));
-      if (!rows) Elem<T>::store(xr + i, v);
+  if (VEC) {
+    constexpr int N = Pack<T>::N;
+    for (int i = threadIdx.x * N; i < hidden; i += blockDim.x * N) {
+      float v[N];
+      Pack<T>::load(xr + i, v);
+      if (dr) {
+        float d[N];
+        Pack<T>::load(dr + i, d);
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[j] = Elem<T>::round(v[j] + d[j]);
+        if (!rows) Pack<T>::store(xr + i, v);
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) { row_vals[i + j] = v[j]; ss += v[j] * v[j]; }
     }
-    row_vals[i] = v;
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = Elem<T>::load(xr + i);
+      if (dr) {
+        v = Elem<T>::round(v + Elem<T>::load(dr + i));
+        if (!rows) Elem<T>::store(xr + i, v);
+      }
+      row_vals[i] = v;
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* o = out + (size_t)blockIdx.x * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    Elem<T>::store(o + i, weight[i] * Elem<T>::round(row_vals[i] * inv));
+  if (VEC) {
+    constexpr int N = Pack<T>::N;
+    for (int i = threadIdx.x * N; i < hidden; i += blockDim.x * N) {
+      float v[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = weight[i + j] * Elem<T>::round(row_vals[i + j] * inv);
+      Pack<T>::store(o + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      Elem<T>::store(o + i, weight[i] * Elem<T>::round(row_vals[i] * inv));
+  }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(void* x, const void* delta, const float* weight, void* out, const int* rows, int n_rows,
+                              int hidden, float eps, size_t smem, cudaStream_t stream) {
+  constexpr int N = Pack<T>::N;
+  const bool vec = hidden % N == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                   (!delta || (uintptr_t)delta % 16 == 0);
+  // the sum's order depends on the block size only, and that depends on the width only
+  int threads = vec ? ((hidden / N + 31) / 32) * 32 : (hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128));
+  if (threads > 512) threads = 512;
+  if (threads < 32) threads = 32;
+  if (vec) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    lb_launch(add_rmsnorm_kernel<T, true>, n_rows, threads, smem, stream, (T*)x, (const T*)delta, weight, (T*)out, rows,
+              hidden, eps);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    lb_launch(add_rmsnorm_kernel<T, false>, n_rows, threads, smem, stream, (T*)x, (const T*)delta, weight, (T*)out, rows,
+              hidden, eps);
+  }
+  return lb_last_error();
 }
 
 LB_EXPORT int lb_add_rmsnorm(int dtype, void* x, const void* delta, const float* weight, void* out,
@@ -61,20 +151,9 @@ LB_EXPORT int lb_add_rmsnorm(int dtype, void* x, const void* delta, const float*
   if (n_rows <= 0) return 0;
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
   if (smem > 200 * 1024) return LB_ERR_SIZE;
-  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  if (dtype == LB_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>((float*)x, (const float*)delta, weight,
-                                                                   (float*)out, rows, hidden, eps);
-  } else if (dtype == LB_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<bf16><<<n_rows, threads, smem, stream>>>((bf16*)x, (const bf16*)delta, weight, (bf16*)out,
-                                                                  rows, hidden, eps);
-  } else
-    return LB_ERR_DTYPE;
-  return lb_last_error();
+  if (dtype == LB_F32) return launch_add_rmsnorm<float>(x, delta, weight, out, rows, n_rows, hidden, eps, smem, stream);
+  if (dtype == LB_BF16) return launch_add_rmsnorm<bf16>(x, delta, weight, out, rows, n_rows, hidden, eps, smem, stream);
+  return LB_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------- QK-norm + rotary + KV write
@@ -96,6 +175,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
                                        const int* __restrict__ positions, const int* __restrict__ slot_map,
                                        int tokens, int q_heads, int kv_heads, int dim, int n_freq, int page_tokens,
                                        float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int heads = q_heads + 2 * kv_heads;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= tokens * heads) return;
@@ -181,11 +262,11 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
   const int threads = 256;
   const long blocks = (warps * 32 + threads - 1) / threads;
   if (dtype == LB_F32)
-    qk_norm_rope_kv_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+    lb_launch(qk_norm_rope_kv_kernel<float>, (unsigned)blocks, threads, 0, stream, 
         (float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, q_norm_w, k_norm_w, inv_freq, positions,
         slot_map, tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps);
   else if (dtype == LB_BF16)
-    qk_norm_rope_kv_kernel<bf16><<<(unsigned)blocks, threads, 0, stream>>>(
+    lb_launch(qk_norm_rope_kv_kernel<bf16>, (unsigned)blocks, threads, 0, stream, 
         (bf16*)qkv, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, q_norm_w, k_norm_w, inv_freq, positions, slot_map,
         tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps);
   else
@@ -198,6 +279,8 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
 // product each round to T (layover/model.py:152-153).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long total, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long t = idx / inter;
@@ -214,9 +297,9 @@ LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, i
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   if (dtype == LB_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
+    lb_launch(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, inter);
   else if (dtype == LB_BF16)
-    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
+    lb_launch(swiglu_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, inter);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -54,6 +54,8 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restr
                  long lda, long ldw, long ldc, bool vec_a, bool vec_w) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[TM][TN];
@@ -105,14 +107,14 @@ LB_EXPORT int lb_gemm_simt(int in_dtype, int out_dtype, const void* A, const voi
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return LB_ERR_SIZE;
   if (in_dtype == LB_F32 && out_dtype == LB_F32)
-    gemm_simt_kernel<float, float><<<grid, THREADS, 0, stream>>>((const float*)A, (const float*)W, (float*)C, M, N, K,
+    lb_launch(gemm_simt_kernel<float, float>, grid, THREADS, 0, stream, (const float*)A, (const float*)W, (float*)C, M, N, K,
                                                                  lda, ldw, ldc, vec_ok<float>(A, lda),
                                                                  vec_ok<float>(W, ldw));
   else if (in_dtype == LB_BF16 && out_dtype == LB_BF16)
-    gemm_simt_kernel<bf16, bf16><<<grid, THREADS, 0, stream>>>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda,
+    lb_launch(gemm_simt_kernel<bf16, bf16>, grid, THREADS, 0, stream, (const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda,
                                                                ldw, ldc, vec_ok<bf16>(A, lda), vec_ok<bf16>(W, ldw));
   else if (in_dtype == LB_BF16 && out_dtype == LB_F32)
-    gemm_simt_kernel<bf16, float><<<grid, THREADS, 0, stream>>>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K,
+    lb_launch(gemm_simt_kernel<bf16, float>, grid, THREADS, 0, stream, (const bf16*)A, (const bf16*)W, (float*)C, M, N, K,
                                                                 lda, ldw, ldc, vec_ok<bf16>(A, lda),
                                                                 vec_ok<bf16>(W, ldw));
   else

@@ -133,22 +133,26 @@ template <> __device__ __forceinline__ void store_row16<bf16>(bf16* p, const flo
   reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-template <int BN> struct Tile {
+// The few-token orientation keeps two blocks on an SM (half the shared memory each), so that a
+// weight matrix with about as many tiles as SMs, or one split in two, still runs in one wave.
+template <int BN, bool SWAP> struct Tile {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
+  static constexpr int BUDGET = SWAP ? SMEM_BUDGET / 2 : SMEM_BUDGET;
+  static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
+  static constexpr int BLOCKS_PER_SM = SWAP ? 2 : 1;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
 // D[i, j] = sum_k Aop[i, k] Bop[j, k], i on the 128-row side. SWAP false: C[i, j] = D; true: C[j, i] = D.
 template <int BN, bool SWAP, typename OutT>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, Tile<BN, SWAP>::BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, int K, int splits,
                     float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok) {
-  using T = Tile<BN>;
+  using T = Tile<BN, SWAP>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles_a = smem;
@@ -178,9 +182,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   if (warp == 0 && lane == 0) {
-    // ---------------- producer
-    for (int i = 0; i < n_kb; ++i) {
+    // ---------------- producer. The weights are written by no kernel, so the first ring of weight
+    // tiles is requested before waiting for the kernel that produces the activations.
+    const int early = n_kb < T::STAGES ? n_kb : T::STAGES;
+    for (int i = 0; i < early; ++i) {
+      mbar_expect_tx(&full[i], T::STAGE_BYTES);
+      if (SWAP) tma_load_2d(tiles_a + i * T::A_BYTES, &map_a, &full[i], (kb_begin + i) * BK, m0);
+      else tma_load_2d(tiles_b + i * T::B_BYTES, &map_b, &full[i], (kb_begin + i) * BK, n0);
+    }
+    pdl_wait();
+    for (int i = 0; i < early; ++i) {
+      if (SWAP) tma_load_2d(tiles_b + i * T::B_BYTES, &map_b, &full[i], (kb_begin + i) * BK, n0);
+      else tma_load_2d(tiles_a + i * T::A_BYTES, &map_a, &full[i], (kb_begin + i) * BK, m0);
+    }
+    for (int i = early; i < n_kb; ++i) {
       const int s = i % T::STAGES;
       const uint32_t phase = (i / T::STAGES) & 1;
       if (!mbar_wait(&empty[s], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 1); flag[0] = 1; break; }
@@ -206,6 +223,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (ok) umma_commit(tmem_full);
   }
   __syncwarp();
+  pdl_wait();   // the epilogue writes memory that earlier kernels may still be reading
 
   // ---------------- epilogue: every warp reads its 32 lanes of the accumulator
   const bool ready = mbar_wait(tmem_full, 0);
@@ -260,11 +278,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       __threadfence();
       const float* tile_partials = partials + (size_t)tile_id * splits * BN * BM;
       if (m0 + row < rows_a) {
-        for (int j = 0; j < valid_cols; ++j) {
-          float sum = 0.f;
-          for (int s = 0; s < splits; ++s) sum += tile_partials[((size_t)s * BN + j) * BM + row];
-          if (SWAP) store_one<OutT>(C + (size_t)(n0 + j) * ldc + m0 + row, sum);
-          else store_one<OutT>(C + (size_t)(m0 + row) * ldc + n0 + j, sum);
+        // eight columns and four splits at a time: those 32 loads do not depend on one another,
+        // and every element is still summed in split order
+        for (int j0 = 0; j0 < valid_cols; j0 += 8) {
+          float sum[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) sum[u] = 0.f;
+          for (int s0 = 0; s0 < splits; s0 += 4) {
+            float part[4][8];
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds) {
+              const float* src = tile_partials + ((size_t)(s0 + ds) * BN + j0) * BM + row;
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                part[ds][u] = (s0 + ds < splits && j0 + u < valid_cols) ? src[(size_t)u * BM] : 0.f;
+            }
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+              for (int u = 0; u < 8; ++u) sum[u] += part[ds][u];
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (j0 + u < valid_cols) {
+              if (SWAP) store_one<OutT>(C + (size_t)(n0 + j0 + u) * ldc + m0 + row, sum[u]);
+              else store_one<OutT>(C + (size_t)(m0 + row) * ldc + n0 + j0 + u, sum[u]);
+            }
+          }
         }
       }
       if (threadIdx.x == 0) counters[tile_id] = 0;   // ready for the next launch
@@ -314,7 +354,7 @@ bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, in
 template <int BN, bool SWAP, typename OutT>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, int rows_a, int rows_b, int K,
            int splits, float* partials, unsigned* counters, bool vector_ok, cudaStream_t stream) {
-  using T = Tile<BN>;
+  using T = Tile<BN, SWAP>;
   auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT>;
   static bool configured = false;
   if (!configured) {
@@ -323,9 +363,9 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
     configured = true;
   }
   dim3 grid((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, splits);
-  kernel<<<grid, THREADS, T::SMEM, stream>>>(map_a, map_b, (OutT*)C, ldc, rows_a, rows_b, K, splits, partials, counters,
-                                             vector_ok);
-  return lb_last_error();
+  const int code = lb_launch(kernel, grid, dim3(THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc, rows_a,
+                             rows_b, K, splits, partials, counters, vector_ok);
+  return code ? code : lb_last_error();
 }
 
 template <bool SWAP, typename OutT>
@@ -358,10 +398,10 @@ LB_EXPORT int lb_gemm_tcgen05_supports(const void* A, const void* W, int K, long
 
 // C[M, N] = A[M, K] W[N, K]^T. out_dtype: LB_BF16 or LB_F32. `scratch` (floats) and `counters`
 // (zeroed once by the caller, `n_counters` of them) serve the split-K path; without them K is
-// never split. `sm_count` sizes the split.
+// never split. `sm_count` sizes the split; `max_splits` > 0 caps it.
 LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K, long lda,
                               long ldw, long ldc, float* scratch, long scratch_floats, unsigned* counters,
-                              int n_counters, int sm_count, cudaStream_t stream) {
+                              int n_counters, int sm_count, int max_splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lb_gemm_tcgen05_supports(A, W, K, lda, ldw)) return LB_ERR_ALIGN;
   if (out_dtype != LB_BF16 && out_dtype != LB_F32) return LB_ERR_DTYPE;
@@ -374,9 +414,17 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
     if (!make_map(&map_a, W, N, K, ldw, BM) || !make_map(&map_b, A, M, K, lda, bn)) return LB_ERR_ALIGN;
     const int tiles = (N + BM - 1) / BM;
     const int total_kb = (K + BK - 1) / BK;
-    if (scratch && counters && tiles <= n_counters && tiles * 4 < sm_count * 3) {
-      splits = sm_count / tiles;
+    if (scratch && counters && tiles <= n_counters && tiles < sm_count) {
+      // One block per SM streams a weight matrix at close to full bandwidth, and every further
+      // split adds a partial tile to write, a fence, a counter and a longer sum, which at these
+      // sizes cost more than the extra blocks win (measured on 2560..9728-wide weights: 8 splits
+      // of a 20-tile matrix beat 15; a 152-tile matrix is fastest unsplit). Wider token tiles
+      // make the partial tiles bigger, so they split less.
+      const int cap = bn <= 16 ? 8 : (bn <= 32 ? 4 : 2);
+      splits = (sm_count + tiles - 1) / tiles;
+      if (splits > cap) splits = cap;
       if (splits > total_kb / 4) splits = total_kb / 4;         // at least four K blocks per split
+      if (max_splits > 0 && splits > max_splits) splits = max_splits;
       const long per_split = (long)tiles * bn * BM;
       if (splits > 1 && per_split * splits > scratch_floats) splits = (int)(scratch_floats / per_split);
       if (splits < 1) splits = 1;

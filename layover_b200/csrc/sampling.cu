@@ -36,6 +36,8 @@ sample_kernel(const float* __restrict__ logits, long row_stride, int vocab, cons
               const uint32_t* __restrict__ step, int* __restrict__ tokens) {
   __shared__ float best_val[THREADS / 32];
   __shared__ int best_idx[THREADS / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* lg = logits + (long)row * row_stride;
   const float temp = temperature ? temperature[row] : 0.f;
@@ -85,6 +87,6 @@ LB_EXPORT int lb_sample(const float* logits, long row_stride, int rows, int voca
                         cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return LB_ERR_SIZE;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, seed_lo, seed_hi, step, tokens);
+  lb_launch(sample_kernel, rows, THREADS, 0, stream, logits, row_stride, vocab, temperature, seed_lo, seed_hi, step, tokens);
   return lb_last_error();
 }

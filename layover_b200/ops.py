@@ -239,7 +239,7 @@ def gemm_tcgen05_supports(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1)
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, max_splits: int = 0) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores; bfloat16 in, out bfloat16 or float32."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
         raise ValueError("gemm_tcgen05: operands must be 2-D bfloat16")
@@ -250,9 +250,10 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
     partials, counters, sms = gemm_scratch(a.device)
     fn = _fn("gemm_tcgen05", "lb_gemm_tcgen05",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_void_p, c_long,
-              c_void_p, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
-              _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), sms, _stream()), "gemm_tcgen05")
+              _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), sms, int(max_splits), _stream()),
+           "gemm_tcgen05")
     return out
 
 
@@ -314,8 +315,8 @@ def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, t
 def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> int:
     """How many ways to split the context so that about two blocks per SM are in flight."""
     natural = n_seqs * kv_heads
-    splits = max(1, -(-2 * sm_count // natural))
-    splits = min(splits, max(1, -(-max_context // 256)))      # at least 256 keys per split
+    splits = max(1, 2 * sm_count // natural)                  # all blocks resident at once, two per SM
+    splits = min(splits, 128, max(1, max_context // 192))     # at least three 64-key tiles per split
     while splits > 1 and n_seqs * q_heads * splits * (dim + 2) > _ATTN_SCRATCH_FLOATS:
         splits -= 1
     return splits
