@@ -157,7 +157,8 @@ LB_EXPORT int lb_add_rmsnorm(int dtype, void* x, const void* delta, const float*
 }
 
 // ---------------------------------------------------------------- QK-norm + rotary + KV write
-// One warp per (token, head) of the fused projection row [q heads | k heads | v heads] x dim.
+// One warp per (token, head) of the fused projection row [q heads | k heads | v heads] x dim
+// (dim a multiple of 8, up to 256; rows, outputs and pages 16-byte aligned).
 //   q, k: per-head RMSNorm over dim (weight shared by the heads, layover/model.py:124-125), then
 //         x*cos + rotate_half(x)*sin with angle = pos * inv_freq[i], cos/sin rounded to T
 //         (layover/model.py:100-102,127-128,193-197); dims >= 2*n_freq pass through unrotated.
@@ -167,7 +168,27 @@ LB_EXPORT int lb_add_rmsnorm(int dtype, void* x, const void* delta, const float*
 // Null norm weights skip the norm, null inv_freq skips the rotation, null pools skip the write
 // (then k is written back in place into the projection row, for a position encoding that runs
 // as a separate step), a null q_out skips the q heads (the pass that only writes pages).
-#define QKV_MAX_PER_LANE 8  // dim <= 256
+// four elements of each half per lane (dim <= 256), one 8- or 16-byte access each
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { Pack<float>::load(p, v); }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { Pack<float>::store(p, v); }
+};
+template <> struct Quad<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&a);
+    w.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = w;
+  }
+};
+
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, const float* __restrict__ q_norm_w,
@@ -200,54 +221,57 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
       dst = src;
     }
   }
+  const int i0 = lane * 4;       // this lane's four lanes of each half
+  const bool mine = i0 < half;
   if (!is_q && !is_k) {  // v: a copy
-    if (dst != src)
-      for (int i = lane; i < dim; i += 32) dst[i] = src[i];
+    if (dst != src && mine) {
+      float a[4], b[4];
+      Quad<T>::load(src + i0, a);
+      Quad<T>::load(src + i0 + half, b);
+      Quad<T>::store(dst + i0, a);
+      Quad<T>::store(dst + i0 + half, b);
+    }
     return;
   }
-  // lane holds pairs (i, i + half) for i = lane, lane + 32, ...
-  float lo[QKV_MAX_PER_LANE / 2], hi[QKV_MAX_PER_LANE / 2];
+  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
   float ss = 0.f;
+  if (mine) {
+    Quad<T>::load(src + i0, lo);
+    Quad<T>::load(src + i0 + half, hi);
 #pragma unroll
-  for (int j = 0; j < QKV_MAX_PER_LANE / 2; ++j) {
-    const int i = lane + 32 * j;
-    lo[j] = hi[j] = 0.f;
-    if (i < half) {
-      lo[j] = Elem<T>::load(src + i);
-      hi[j] = Elem<T>::load(src + i + half);
-      ss += lo[j] * lo[j] + hi[j] * hi[j];
-    }
+    for (int j = 0; j < 4; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
   }
   const float* w = is_q ? q_norm_w : k_norm_w;
   if (w) {
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    if (mine) {
 #pragma unroll
-    for (int j = 0; j < QKV_MAX_PER_LANE / 2; ++j) {
-      const int i = lane + 32 * j;
-      if (i < half) {
-        lo[j] = Elem<T>::round(w[i] * Elem<T>::round(lo[j] * inv));
-        hi[j] = Elem<T>::round(w[i + half] * Elem<T>::round(hi[j] * inv));
+      for (int j = 0; j < 4; ++j) {
+        lo[j] = Elem<T>::round(w[i0 + j] * Elem<T>::round(lo[j] * inv));
+        hi[j] = Elem<T>::round(w[i0 + j + half] * Elem<T>::round(hi[j] * inv));
       }
     }
   }
-  const float pos = (float)positions[t];
+  if (!mine) return;
+  if (inv_freq) {
+    const float pos = (float)positions[t];
 #pragma unroll
-  for (int j = 0; j < QKV_MAX_PER_LANE / 2; ++j) {
-    const int i = lane + 32 * j;
-    if (i < half) {
-      float a = lo[j], b = hi[j];
-      if (inv_freq && i < n_freq) {
-        const float angle = pos * inv_freq[i];
-        const float c = Elem<T>::round(cosf(angle)), s = Elem<T>::round(sinf(angle));
+    for (int j = 0; j < 4; ++j) {
+      if (i0 + j < n_freq) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i0 + j], &sn, &cs);
+        const float c = Elem<T>::round(cs), s = Elem<T>::round(sn);
         // rotate_half(x) = (-hi, lo): each product and the sum round to T
-        a = Elem<T>::round(Elem<T>::round(lo[j] * c) + Elem<T>::round(-hi[j] * s));
-        b = Elem<T>::round(Elem<T>::round(hi[j] * c) + Elem<T>::round(lo[j] * s));
+        const float a = Elem<T>::round(Elem<T>::round(lo[j] * c) + Elem<T>::round(-hi[j] * s));
+        const float b = Elem<T>::round(Elem<T>::round(hi[j] * c) + Elem<T>::round(lo[j] * s));
+        lo[j] = a;
+        hi[j] = b;
       }
-      Elem<T>::store(dst + i, a);
-      Elem<T>::store(dst + i + half, b);
     }
   }
+  Quad<T>::store(dst + i0, lo);
+  Quad<T>::store(dst + i0 + half, hi);
 }
 
 LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool, void* v_pool,
@@ -255,7 +279,7 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
                                  const int* positions, const int* slot_map, int tokens, int q_heads, int kv_heads,
                                  int dim, int n_freq, int page_tokens, float eps, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (dim % 2 || dim > 32 * QKV_MAX_PER_LANE || 2 * n_freq > dim) return LB_ERR_SIZE;
+  if (dim % 8 || dim > 256 || 2 * n_freq > dim) return LB_ERR_SIZE;   // four elements of each half per lane
   // a rotation pairs i with i + dim/2 only when the rotary part spans the whole head
   if (inv_freq && 2 * n_freq != dim) return LB_ERR_SIZE;
   const long warps = (long)tokens * (q_heads + 2 * kv_heads);
@@ -277,30 +301,45 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
 // ---------------------------------------------------------------- SwiGLU
 // out[t, j] = silu(gu[t, j]) * gu[t, inter + j], silu(z) = z / (1 + exp(-z)); silu and the
 // product each round to T (layover/model.py:152-153).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long total, int inter) {
   pdl_launch_dependents();
   pdl_wait();
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int N = VEC ? Pack<T>::N : 1;
+  const long idx = ((long)blockIdx.x * blockDim.x + threadIdx.x) * N;
   if (idx >= total) return;
   const long t = idx / inter;
-  const int j = (int)(idx % inter);
-  const float g = Elem<T>::load(gate_up + t * 2 * inter + j);
-  const float u = Elem<T>::load(gate_up + t * 2 * inter + inter + j);
-  const float s = Elem<T>::round(g / (1.0f + expf(-g)));
-  Elem<T>::store(out + idx, s * u);
+  const int j = (int)(idx - t * inter);
+  const T* gp = gate_up + t * 2 * inter + j;
+  if (VEC) {
+    float g[Pack<T>::N], u[Pack<T>::N];
+    Pack<T>::load(gp, g);
+    Pack<T>::load(gp + inter, u);
+#pragma unroll
+    for (int i = 0; i < Pack<T>::N; ++i) g[i] = Elem<T>::round(g[i] / (1.0f + expf(-g[i]))) * u[i];
+    Pack<T>::store(out + idx, g);
+  } else {
+    const float g = Elem<T>::load(gp), u = Elem<T>::load(gp + inter);
+    Elem<T>::store(out + idx, Elem<T>::round(g / (1.0f + expf(-g))) * u);
+  }
+}
+
+template <typename T>
+static int launch_swiglu(const void* gate_up, void* out, long total, int inter, cudaStream_t stream) {
+  constexpr int N = Pack<T>::N;
+  const bool vec = inter % N == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0;
+  const int threads = 256;
+  const long work = vec ? total / N : total;
+  const unsigned blocks = (unsigned)((work + threads - 1) / threads);
+  if (vec) lb_launch(swiglu_kernel<T, true>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter);
+  else lb_launch(swiglu_kernel<T, false>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter);
+  return lb_last_error();
 }
 
 LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, int inter, cudaStream_t stream) {
   const long total = (long)tokens * inter;
   if (total <= 0) return 0;
-  const int threads = 256;
-  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  if (dtype == LB_F32)
-    lb_launch(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, inter);
-  else if (dtype == LB_BF16)
-    lb_launch(swiglu_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, inter);
-  else
-    return LB_ERR_DTYPE;
-  return lb_last_error();
+  if (dtype == LB_F32) return launch_swiglu<float>(gate_up, out, total, inter, stream);
+  if (dtype == LB_BF16) return launch_swiglu<bf16>(gate_up, out, total, inter, stream);
+  return LB_ERR_DTYPE;
 }
