@@ -32,7 +32,11 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "sampling": ("sampling.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),
+    "decode_attention_static": ("decode_attention_static.cu", ()),
 }
+
+# .cu files that a source includes (their text is part of the library's hash)
+INCLUDED_SOURCES: dict[str, tuple[str, ...]] = {"decode_attention_static": ("attention_mma.cu",)}
 
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -62,6 +66,8 @@ def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + SOURCES[name][1]).encode())
     h.update((HERE / SOURCES[name][0]).read_bytes())
+    for included in INCLUDED_SOURCES.get(name, ()):
+        h.update((HERE / included).read_bytes())
     for header in sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h")):
         h.update(header.name.encode())
         h.update(header.read_bytes())
