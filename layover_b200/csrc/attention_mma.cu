@@ -129,16 +129,124 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* _
   }
 }
 
+// ------------------------------------------------------------------------------- one warp, one tile
+__device__ __forceinline__ void ldmatrix_x4_at(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_at(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// The 16 query rows of one warp against PAIRS * 16 keys of a tile in shared memory:
+// scores, mask, running maximum and sum, P V. `k_addr` / `v_addr` are shared-memory byte addresses
+// of the warp's first key row plus this lane's ldmatrix offset; with EXACT the head size equals
+// MAX_DIM and every address offset is a constant. UPPER false skips the softmax of rows 8..15
+// (decode with at most 8 query heads per KV head). `masked` false skips the comparisons for a
+// tile that every row sees completely. Scores stay unscaled; the scale enters the exponent.
+template <int MAX_DIM, bool EXACT, int PAIRS, bool UPPER>
+__device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4], uint32_t k_addr, uint32_t v_addr,
+                                          int dim, float (&o)[MAX_DIM / 8][4], float (&m_run)[2], float (&l_run)[2],
+                                          bool masked, int key0, int p0, int p1, int key_lo, int window, float c,
+                                          int t) {
+  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, NT_S = PAIRS * 2;
+  const int dk = EXACT ? KSTEPS : (dim >> 4);
+  const uint32_t row_bytes = (uint32_t)((EXACT ? MAX_DIM : dim) + PAD) * 2;
+  float s[NT_S][4];
+#pragma unroll
+  for (int n = 0; n < NT_S; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    if (EXACT || k < dk) {
+#pragma unroll
+      for (int n2 = 0; n2 < PAIRS; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4_at(b, k_addr + n2 * 16 * row_bytes + k * 32);
+        mma_bf16(s[2 * n2], qf[k], b[0], b[1]);
+        mma_bf16(s[2 * n2 + 1], qf[k], b[2], b[3]);
+      }
+    }
+  }
+  if (masked) {
+#pragma unroll
+    for (int n = 0; n < NT_S; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (!UPPER && e >= 2) continue;
+        const int key = key0 + n * 8 + 2 * t + (e & 1);
+        const int p = e < 2 ? p0 : p1;
+        const bool seen = key <= p && key >= key_lo && (window <= 0 || p - key < window);
+        if (!seen) s[n][e] = -INFINITY;
+      }
+    }
+  }
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int n = 0; n < NT_S; ++n) {
+    tile_max[0] = fmaxf(tile_max[0], fmaxf(s[n][0], s[n][1]));
+    if (UPPER) tile_max[1] = fmaxf(tile_max[1], fmaxf(s[n][2], s[n][3]));
+  }
+  float alpha[2] = {1.f, 1.f}, neg_base[2] = {0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+    const float m_new = fmaxf(m_run[r], tile_max[r]);
+    const float base = m_new == -INFINITY ? 0.f : m_new;
+    alpha[r] = fast_exp2((m_run[r] - base) * c);      // exp2(-inf) = 0 on the first tile
+    neg_base[r] = -base * c;
+    m_run[r] = m_new;
+  }
+  float tile_sum[2] = {0.f, 0.f};
+  uint32_t pf[PAIRS][4];
+#pragma unroll
+  for (int n = 0; n < NT_S; ++n) {
+    const float e0 = fast_exp2(fmaf(s[n][0], c, neg_base[0])), e1 = fast_exp2(fmaf(s[n][1], c, neg_base[0]));
+    tile_sum[0] += e0 + e1;
+    pf[n >> 1][(n & 1) * 2] = pack_bf16(e0, e1);
+    if (UPPER) {
+      const float e2 = fast_exp2(fmaf(s[n][2], c, neg_base[1])), e3 = fast_exp2(fmaf(s[n][3], c, neg_base[1]));
+      tile_sum[1] += e2 + e3;
+      pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2, e3);
+    } else {
+      pf[n >> 1][(n & 1) * 2 + 1] = 0u;
+    }
+  }
+  l_run[0] = l_run[0] * alpha[0] + tile_sum[0];
+  if (UPPER) l_run[1] = l_run[1] * alpha[1] + tile_sum[1];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n) {
+    if (EXACT || n * 8 < dim) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+      if (UPPER) { o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
+    }
+  }
+#pragma unroll
+  for (int kk = 0; kk < PAIRS; ++kk) {
+#pragma unroll
+    for (int n2 = 0; n2 < NT_O / 2; ++n2) {
+      if (EXACT || n2 < dk) {
+        uint32_t b[4];
+        ldmatrix_x4_trans_at(b, v_addr + kk * 16 * row_bytes + n2 * 32);
+        mma_bf16(o[2 * n2], pf[kk], b[0], b[1]);
+        mma_bf16(o[2 * n2 + 1], pf[kk], b[2], b[3]);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------- prefill
-template <int MAX_DIM>
+template <int MAX_DIM, bool EXACT>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                          bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads, int kv_heads,
-                         int dim, int page_tokens, float scale_log2, int window, int chunk_shift, int page_shift) {
-  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, NT_S = BKEYS / 8;
+                         int dim_arg, int page_tokens, float scale_log2, int window, int chunk_shift, int page_shift) {
+  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int dim = EXACT ? MAX_DIM : dim_arg;
   const int stride = dim + PAD;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
   bf16* k_s = q_s + BQ * stride;            // [2][BKEYS][stride]
@@ -180,7 +288,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 #pragma unroll
   for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  const int p_row[2] = {p_first + warp * 16 + g, p_first + warp * 16 + g + 8};   // rows past n_q compute harmlessly
+  const int p_warp = p_first + warp * 16;                   // position of the warp's first row
+  const int p0 = p_warp + g, p1 = p_warp + g + 8;           // rows past n_q compute harmlessly
+  // lane offsets of the ldmatrix rows (bytes): K rows by key, V rows by key with the d-chunk swapped in
+  const uint32_t k_lane = (uint32_t)(((lane >> 4) * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8) * 2;
+  const uint32_t v_lane = (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 8) * 2;
+  const uint32_t k_base = smem_u32(k_s) + k_lane, v_base = smem_u32(v_s) + v_lane;
+  const uint32_t buf_bytes = (uint32_t)BKEYS * stride * 2;
 
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int buf = (tile - tile_lo) & 1;
@@ -196,81 +310,15 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     if (tile == tile_lo) {
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k)
-        if (k < dk) ldmatrix_x4(qf[k], q_s + (warp * 16 + (lane & 15)) * stride + k * 16 + (lane >> 4) * 8);
+        if (EXACT || k < dk) ldmatrix_x4(qf[k], q_s + (warp * 16 + (lane & 15)) * stride + k * 16 + (lane >> 4) * 8);
     }
-    const bf16* kt = k_s + buf * BKEYS * stride;
-    const bf16* vt = v_s + buf * BKEYS * stride;
-
     // a warp whose rows all lie before this tile has nothing to do in it
-    const bool warp_active = tile * BKEYS <= p_first + warp * 16 + 15;
-    if (warp_active) {
-      float s[NT_S][4];
-#pragma unroll
-      for (int n = 0; n < NT_S; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-#pragma unroll
-      for (int k = 0; k < KSTEPS; ++k) {
-        if (k < dk) {
-#pragma unroll
-          for (int n2 = 0; n2 < NT_S / 2; ++n2) {
-            uint32_t b[4];
-            ldmatrix_x4(b, kt + (n2 * 16 + (lane >> 4) * 8 + (lane & 7)) * stride + k * 16 + ((lane >> 3) & 1) * 8);
-            mma_bf16(s[2 * n2], qf[k], b[0], b[1]);
-            mma_bf16(s[2 * n2 + 1], qf[k], b[2], b[3]);
-          }
-        }
-      }
-      // mask from absolute positions, running maximum and sum per row (two rows per thread)
-      float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int n = 0; n < NT_S; ++n) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = tile * BKEYS + n * 8 + 2 * t + (e & 1);
-          const int p = p_row[e >> 1];
-          const bool seen = key <= p && (window <= 0 || p - key < window);
-          s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
-          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[n][e]);
-        }
-      }
-      float alpha[2], base[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-        const float m_new = fmaxf(m_run[r], tile_max[r]);
-        base[r] = m_new == -INFINITY ? 0.f : m_new;
-        alpha[r] = fast_exp2(m_run[r] - base[r]);      // exp2(-inf) = 0 on the first tile
-        m_run[r] = m_new;
-      }
-      float tile_sum[2] = {0.f, 0.f};
-      uint32_t pf[NT_S / 2][4];
-#pragma unroll
-      for (int n = 0; n < NT_S; ++n) {
-        const float p0 = fast_exp2(s[n][0] - base[0]), p1 = fast_exp2(s[n][1] - base[0]);
-        const float p2 = fast_exp2(s[n][2] - base[1]), p3 = fast_exp2(s[n][3] - base[1]);
-        tile_sum[0] += p0 + p1;
-        tile_sum[1] += p2 + p3;
-        pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
-        pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
-      }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + tile_sum[r];
-#pragma unroll
-      for (int n = 0; n < NT_O; ++n) {
-        o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
-      }
-#pragma unroll
-      for (int kk = 0; kk < BKEYS / 16; ++kk) {
-#pragma unroll
-        for (int n2 = 0; n2 < NT_O / 2; ++n2) {
-          if (n2 < dk) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, vt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * stride + n2 * 16 + (lane >> 4) * 8);
-            mma_bf16(o[2 * n2], pf[kk], b[0], b[1]);
-            mma_bf16(o[2 * n2 + 1], pf[kk], b[2], b[3]);
-          }
-        }
-      }
+    if (tile * BKEYS <= p_warp + 15) {
+      // every row of the warp sees the whole tile unless it reaches past the first row's position,
+      // starts before the first visible key or a window cuts it
+      const bool masked = tile * BKEYS + BKEYS - 1 > p_warp || tile * BKEYS < key_lo || window > 0;
+      warp_tile<MAX_DIM, EXACT, BKEYS / 16, true>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run,
+                                                  l_run, masked, tile * BKEYS, p0, p1, key_lo, window, scale_log2, t);
     }
     __syncthreads();   // the buffer may be overwritten by the next iteration's prefetch
   }
@@ -288,7 +336,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     bf16* dst = out + ((size_t)(row0 + q0 + row) * q_heads + head) * dim;
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) {
-      if (n * 8 < dim)
+      if (EXACT || n * 8 < dim)
         *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
     }
   }
@@ -296,16 +344,17 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
 // ------------------------------------------------------------------------------- decode
 // Rows 0..group-1 of the 16-row tile are the query heads of one KV head (group <= 16).
-template <int MAX_DIM>
+template <int MAX_DIM, bool EXACT, bool UPPER>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
-                        const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim, int page_tokens,
+                        const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim_arg, int page_tokens,
                         float scale_log2, int window, int splits, float* __restrict__ partials,
                         unsigned* __restrict__ counters, int chunk_shift, int page_shift) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, STAGES = 3;
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int dim = EXACT ? MAX_DIM : dim_arg;
   const int stride = dim + PAD;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);          // [16][stride]
   bf16* k_s = q_s + 16 * stride;                          // [STAGES][BKEYS][stride]
@@ -356,6 +405,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
   for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const uint32_t k_lane = (uint32_t)((warp * 16 + (lane >> 4) * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8) * 2;
+  const uint32_t v_lane = (uint32_t)((warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 8) * 2;
+  const uint32_t k_base = smem_u32(k_s) + k_lane, v_base = smem_u32(v_s) + v_lane;
+  const uint32_t buf_bytes = (uint32_t)BKEYS * stride * 2;
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int i = tile - tile_begin, buf = i % STAGES;
@@ -370,69 +423,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     if (i == 0) {
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k)
-        if (k < dk) ldmatrix_x4(qf[k], q_s + (lane & 15) * stride + k * 16 + (lane >> 4) * 8);
+        if (EXACT || k < dk) ldmatrix_x4(qf[k], q_s + (lane & 15) * stride + k * 16 + (lane >> 4) * 8);
     }
-    const bf16* kt = k_s + buf * BKEYS * stride + warp * 16 * stride;   // this warp's 16 keys of the tile
-    const bf16* vt = v_s + buf * BKEYS * stride + warp * 16 * stride;
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-    for (int k = 0; k < KSTEPS; ++k) {
-      if (k < dk) {
-        uint32_t b[4];
-        ldmatrix_x4(b, kt + ((lane >> 4) * 8 + (lane & 7)) * stride + k * 16 + ((lane >> 3) & 1) * 8);
-        mma_bf16(s[0], qf[k], b[0], b[1]);
-        mma_bf16(s[1], qf[k], b[2], b[3]);
-      }
-    }
-    float tile_max = -INFINITY;   // every row has the same position, so one mask serves both rows
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = tile * BKEYS + warp * 16 + n * 8 + 2 * t + (e & 1);
-        const bool seen = key <= p && key >= key_lo;
-        s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
-      }
-    }
-    float row_max[2] = {fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])),
-                        fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]))};
-    float alpha[2], base[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 1));
-      row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 2));
-      const float m_new = fmaxf(m_run[r], row_max[r]);
-      base[r] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[r] = fast_exp2(m_run[r] - base[r]);
-      m_run[r] = m_new;
-    }
-    (void)tile_max;
-    uint32_t pf[4];
-    float tile_sum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const float p0 = fast_exp2(s[n][0] - base[0]), p1 = fast_exp2(s[n][1] - base[0]);
-      const float p2 = fast_exp2(s[n][2] - base[1]), p3 = fast_exp2(s[n][3] - base[1]);
-      tile_sum[0] += p0 + p1;
-      tile_sum[1] += p2 + p3;
-      pf[n * 2] = pack_bf16(p0, p1);
-      pf[n * 2 + 1] = pack_bf16(p2, p3);
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + tile_sum[r];
-#pragma unroll
-    for (int n = 0; n < NT_O; ++n) {
-      o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
-    }
-#pragma unroll
-    for (int n2 = 0; n2 < NT_O / 2; ++n2) {
-      if (n2 < dk) {
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, vt + (((lane >> 3) & 1) * 8 + (lane & 7)) * stride + n2 * 16 + (lane >> 4) * 8);
-        mma_bf16(o[2 * n2], pf, b[0], b[1]);
-        mma_bf16(o[2 * n2 + 1], pf, b[2], b[3]);
-      }
-    }
+    // only the tile that holds the last key, or the first visible one, needs the comparisons
+    const bool masked = tile * BKEYS + BKEYS - 1 > p || tile * BKEYS < key_lo;
+    warp_tile<MAX_DIM, EXACT, 1, UPPER>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run, l_run, masked,
+                                        tile * BKEYS + warp * 16, p, p, key_lo, 0, scale_log2, t);
     __syncthreads();
   }
   cp_async_wait<0>();
@@ -447,19 +443,20 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   float* merge = reinterpret_cast<float*>(smem_raw);      // [WARPS][16][dim + 2]: output, then max, then sum
   const int mstride = dim + 2;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
     float* dst = merge + ((size_t)warp * 16 + g + 8 * r) * mstride;
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) {
-      if (n * 8 < dim) { dst[n * 8 + 2 * t] = o[n][2 * r]; dst[n * 8 + 2 * t + 1] = o[n][2 * r + 1]; }
+      if (EXACT || n * 8 < dim) { dst[n * 8 + 2 * t] = o[n][2 * r]; dst[n * 8 + 2 * t + 1] = o[n][2 * r + 1]; }
     }
     if (t == 0) { dst[dim] = m_run[r]; dst[dim + 1] = l_run[r]; }
   }
   __syncthreads();
+  const float c = scale_log2;
   const unsigned tile_id = blockIdx.x * gridDim.y + blockIdx.y;
   float* my_partial = partials ? partials + ((size_t)tile_id * splits + split) * group * mstride : nullptr;
   for (int i = threadIdx.x; i < group * dim; i += THREADS) {
-    const int r = i / dim, c = i % dim;
+    const int r = i / dim, col = i % dim;
     float m_all = -INFINITY;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + r) * mstride + dim]);
@@ -468,15 +465,15 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
       const float* src = merge + ((size_t)w * 16 + r) * mstride;
-      const float f = fast_exp2(src[dim] - base);
-      acc += src[c] * f;
+      const float f = fast_exp2((src[dim] - base) * c);
+      acc += src[col] * f;
       l_all += src[dim + 1] * f;
     }
     if (splits == 1) {
-      out[((size_t)row * q_heads + head0 + r) * dim + c] = __float2bfloat16_rn(acc / l_all);
+      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(acc / l_all);
     } else {
-      my_partial[r * mstride + c] = acc;
-      if (c == 0) { my_partial[r * mstride + dim] = m_all; my_partial[r * mstride + dim + 1] = l_all; }
+      my_partial[r * mstride + col] = acc;
+      if (col == 0) { my_partial[r * mstride + dim] = m_all; my_partial[r * mstride + dim + 1] = l_all; }
     }
   }
   if (splits == 1) return;
@@ -493,9 +490,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   // memory first, so that the loads of the second pass do not wait on one another
   float* factor = merge;                                   // [splits][group], then [group] sums
   float* l_total = merge + (size_t)splits * group;
-  __syncthreads();
   float* m_part = l_total + group;                         // [splits][group] maxima, then sums
   float* l_part = m_part + (size_t)splits * group;
+  __syncthreads();
   for (int i = threadIdx.x; i < splits * group; i += THREADS) {   // every (split, row) is its own load
     const float* src = all + (size_t)i * mstride;
     m_part[i] = src[dim];
@@ -508,7 +505,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const float base = m_all == -INFINITY ? 0.f : m_all;
     float l_all = 0.f;
     for (int s = 0; s < splits; ++s) {
-      const float f = fast_exp2(m_part[s * group + r] - base);
+      const float f = fast_exp2((m_part[s * group + r] - base) * c);
       factor[s * group + r] = f;
       l_all += l_part[s * group + r] * f;
     }
@@ -516,11 +513,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   }
   __syncthreads();
   for (int i = threadIdx.x; i < group * dim; i += THREADS) {
-    const int r = i / dim, c = i % dim;
+    const int r = i / dim, col = i % dim;
     float acc = 0.f;
 #pragma unroll 8
-    for (int s = 0; s < splits; ++s) acc += all[((size_t)s * group + r) * mstride + c] * factor[s * group + r];
-    out[((size_t)row * q_heads + head0 + r) * dim + c] = __float2bfloat16_rn(acc / l_total[r]);
+    for (int s = 0; s < splits; ++s) acc += all[((size_t)s * group + r) * mstride + col] * factor[s * group + r];
+    out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(acc / l_total[r]);
   }
   if (threadIdx.x == 0) counters[tile_id] = 0;
 }
@@ -540,6 +537,38 @@ size_t decode_smem(int dim) {
 
 LB_EXPORT int lb_attention_mma_block_queries() { return BQ; }
 
+namespace {
+template <typename Kernel> void allow_smem(Kernel kernel, size_t bytes) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+void configure_once() {
+  static bool done = false;
+  if (done) return;
+  allow_smem(attention_prefill_kernel<128, true>, prefill_smem(128));
+  allow_smem(attention_prefill_kernel<128, false>, prefill_smem(128));
+  allow_smem(attention_prefill_kernel<256, true>, prefill_smem(256));
+  allow_smem(attention_prefill_kernel<256, false>, prefill_smem(256));
+  allow_smem(attention_decode_kernel<128, true, false>, decode_smem(128));
+  allow_smem(attention_decode_kernel<128, true, true>, decode_smem(128));
+  allow_smem(attention_decode_kernel<128, false, true>, decode_smem(128));
+  allow_smem(attention_decode_kernel<256, true, true>, decode_smem(256));
+  allow_smem(attention_decode_kernel<256, false, true>, decode_smem(256));
+  done = true;
+}
+
+// launches the decode kernel instantiation for this head size and group
+template <typename... Args>
+int launch_decode(int dim, int group, dim3 grid, size_t smem, cudaStream_t stream, Args... args) {
+  if (dim == 128) {
+    if (group <= 8) return lb_launch(attention_decode_kernel<128, true, false>, grid, dim3(THREADS), smem, stream, args...);
+    return lb_launch(attention_decode_kernel<128, true, true>, grid, dim3(THREADS), smem, stream, args...);
+  }
+  if (dim < 128) return lb_launch(attention_decode_kernel<128, false, true>, grid, dim3(THREADS), smem, stream, args...);
+  if (dim == 256) return lb_launch(attention_decode_kernel<256, true, true>, grid, dim3(THREADS), smem, stream, args...);
+  return lb_launch(attention_decode_kernel<256, false, true>, grid, dim3(THREADS), smem, stream, args...);
+}
+}  // namespace
+
 // Prompt portions (any number of queries per sequence), listed as tiles of 64 queries.
 LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
@@ -547,24 +576,20 @@ LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const
                                         int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
+  configure_once();
   const size_t smem = prefill_smem(dim);
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
-  dim3 grid(n_tiles, q_heads);
-  if (dim <= 128) {
-    static bool set = false;
-    if (!set) { cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem(128)); set = true; }
-    lb_launch(attention_prefill_kernel<128>, grid, THREADS, smem, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift);
-  } else {
-    static bool set = false;
-    if (!set) { cudaFuncSetAttribute(attention_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem(256)); set = true; }
-    lb_launch(attention_prefill_kernel<256>, grid, THREADS, smem, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift);
-  }
-  return lb_last_error();
+  dim3 grid(n_tiles, q_heads), block(THREADS);
+  int code;
+#define LB_PREFILL_ARGS (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, \
+                        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift
+  if (dim == 128) code = lb_launch(attention_prefill_kernel<128, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+  else if (dim < 128) code = lb_launch(attention_prefill_kernel<128, false>, grid, block, smem, stream, LB_PREFILL_ARGS);
+  else if (dim == 256) code = lb_launch(attention_prefill_kernel<256, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
+  else code = lb_launch(attention_prefill_kernel<256, false>, grid, block, smem, stream, LB_PREFILL_ARGS);
+#undef LB_PREFILL_ARGS
+  return code ? code : lb_last_error();
 }
 
 // Floats of scratch that `splits` splits of `n_seqs` sequences need.
@@ -587,25 +612,15 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
   if (splits > 1 && (!partials || !counters || lb_attention_decode_scratch(n_seqs, q_heads, dim, splits) > partial_floats ||
                      (long)n_seqs * kv_heads > n_counters))
     return LB_ERR_SIZE;
+  configure_once();
   const size_t smem = decode_smem(dim);
   if ((3 * (size_t)splits + 1) * (q_heads / kv_heads) * sizeof(float) > smem) return LB_ERR_SIZE;   // merge factors
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_seqs, kv_heads, splits);
-  if (dim <= 128) {
-    static bool set = false;
-    if (!set) { cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(128)); set = true; }
-    lb_launch(attention_decode_kernel<128>, grid, THREADS, smem, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
-        page_shift);
-  } else {
-    static bool set = false;
-    if (!set) { cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(256)); set = true; }
-    lb_launch(attention_decode_kernel<256>, grid, THREADS, smem, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
-        page_shift);
-  }
-  return lb_last_error();
+  const int code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
+                                 (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
+                                 q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters,
+                                 chunk_shift, page_shift);
+  return code ? code : lb_last_error();
 }

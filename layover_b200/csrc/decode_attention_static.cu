@@ -25,13 +25,7 @@ int scratch_for_current_device(void** address) {
       cudaGetLastError();
       return LB_STATIC_ERR_SETUP;
     }
-    if (cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)decode_smem(128)) != cudaSuccess ||
-        cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)decode_smem(256)) != cudaSuccess) {
-      cudaGetLastError();
-      return LB_STATIC_ERR_SETUP;
-    }
+    configure_once();   // raises the kernels' shared-memory limit; allocates nothing
     g_scratch_address[device] = found;
   }
   *address = g_scratch_address[device];
@@ -68,15 +62,10 @@ int lb_attention_decode_bf16_static(const void* q, const void* k_pool, const voi
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_seqs, kv_heads, splits);
-  int code;
-  if (dim <= 128)
-    code = lb_launch(attention_decode_kernel<128>, grid, dim3(THREADS), smem, stream, (const bf16*)q, (const bf16*)k_pool,
-                     (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, (const int*)nullptr, q_heads,
-                     kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift, page_shift);
-  else
-    code = lb_launch(attention_decode_kernel<256>, grid, dim3(THREADS), smem, stream, (const bf16*)q, (const bf16*)k_pool,
-                     (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, (const int*)nullptr, q_heads,
-                     kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift, page_shift);
+  const int code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
+                                 (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
+                                 (const int*)nullptr, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials,
+                                 counters, chunk_shift, page_shift);
   return code ? code : lb_last_error();
 }
 
