@@ -156,16 +156,40 @@ LB_EXPORT int lb_add_rmsnorm(int dtype, void* x, const void* delta, const float*
   return LB_ERR_DTYPE;
 }
 
+// ---------------------------------------------------------------- rotary tables
+// table[t][0][i] = cos(pos_t * inv_freq[i]), table[t][1][i] = sin(...), 32-bit (layover/model.py:193-197).
+// Made once per step and read by every layer, as the reference makes its tables once per call.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ table, int tokens, int n_freq) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * n_freq) return;
+  const int t = idx / n_freq, i = idx - t * n_freq;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+  table[((size_t)t * 2) * n_freq + i] = cs;
+  table[((size_t)t * 2 + 1) * n_freq + i] = sn;
+}
+
+LB_EXPORT int lb_rope_table(const int* positions, const float* inv_freq, float* table, int tokens, int n_freq,
+                            cudaStream_t stream) {
+  const int total = tokens * n_freq;
+  if (total <= 0) return 0;
+  lb_launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, table, tokens, n_freq);
+  return lb_last_error();
+}
+
 // ---------------------------------------------------------------- QK-norm + rotary + KV write
 // One warp per (token, head) of the fused projection row [q heads | k heads | v heads] x dim
 // (dim a multiple of 8, up to 256; rows, outputs and pages 16-byte aligned).
 //   q, k: per-head RMSNorm over dim (weight shared by the heads, layover/model.py:124-125), then
-//         x*cos + rotate_half(x)*sin with angle = pos * inv_freq[i], cos/sin rounded to T
+//         x*cos + rotate_half(x)*sin with cos/sin from the step's table, rounded to T
 //         (layover/model.py:100-102,127-128,193-197); dims >= 2*n_freq pass through unrotated.
 //   q is written to q_out [tokens, q_heads, dim]; k and v go to their page:
 //         pool[(page * kv_heads + head) * page_tokens + slot][dim], page*page_tokens+slot = slot_map[t]
 //         (layover/model.py:133,139-140).
-// Null norm weights skip the norm, null inv_freq skips the rotation, null pools skip the write
+// Null norm weights skip the norm, a null table skips the rotation, null pools skip the write
 // (then k is written back in place into the projection row, for a position encoding that runs
 // as a separate step), a null q_out skips the q heads (the pass that only writes pages).
 // four elements of each half per lane (dim <= 256), one 8- or 16-byte access each
@@ -189,110 +213,118 @@ template <> struct Quad<bf16> {
   }
 };
 
+// A group of `lanes` lanes (a power of two, dim / 8 rounded up) serves one (token, head); a warp
+// serves 32 / lanes of them at once and two rounds per thread, with the loads of both rounds issued
+// before any arithmetic, so that enough bytes are in flight to keep the memory system busy.
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, const float* __restrict__ q_norm_w,
-                                       const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
-                                       const int* __restrict__ positions, const int* __restrict__ slot_map,
+                                       const float* __restrict__ k_norm_w, const float* __restrict__ rope_table,
+                                       const int* __restrict__ slot_map,
                                        int tokens, int q_heads, int kv_heads, int dim, int n_freq, int page_tokens,
-                                       float eps) {
+                                       float eps, int lanes) {
   pdl_launch_dependents();
   pdl_wait();
-  const int heads = q_heads + 2 * kv_heads;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= tokens * heads) return;
-  const int t = warp / heads, h = warp % heads;
-  T* src = qkv + ((size_t)t * heads + h) * dim;
-  const bool is_q = h < q_heads, is_k = !is_q && h < q_heads + kv_heads;
-  const int half = dim >> 1;
-
-  T* dst;
-  if (is_q) {
-    if (!q_out) return;  // a second pass that only writes pages
-    dst = q_out + ((size_t)t * q_heads + h) * dim;
-  } else {
-    T* pool = is_k ? k_pool : v_pool;
-    if (pool) {
-      const int kvh = is_k ? h - q_heads : h - q_heads - kv_heads;
-      const int slot = slot_map[t];
-      const size_t page = slot / page_tokens, within = slot % page_tokens;
-      dst = pool + ((page * kv_heads + kvh) * page_tokens + within) * dim;
-    } else {
-      dst = src;
-    }
-  }
-  const int i0 = lane * 4;       // this lane's four lanes of each half
+  constexpr int ROUNDS = 2;
+  const int heads = q_heads + 2 * kv_heads, half = dim >> 1;
+  const int per_warp = 32 / lanes;
+  const int lane = threadIdx.x & 31, sub = lane / lanes, i0 = (lane % lanes) * 4;
+  const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long total = (long)tokens * heads;
   const bool mine = i0 < half;
-  if (!is_q && !is_k) {  // v: a copy
-    if (dst != src && mine) {
-      float a[4], b[4];
-      Quad<T>::load(src + i0, a);
-      Quad<T>::load(src + i0 + half, b);
-      Quad<T>::store(dst + i0, a);
-      Quad<T>::store(dst + i0 + half, b);
-    }
-    return;
-  }
-  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-  float ss = 0.f;
-  if (mine) {
-    Quad<T>::load(src + i0, lo);
-    Quad<T>::load(src + i0 + half, hi);
+
+  long item[ROUNDS];
+  float lo[ROUNDS][4], hi[ROUNDS][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+  for (int r = 0; r < ROUNDS; ++r) {
+    item[r] = (warp * ROUNDS + r) * per_warp + sub;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) lo[r][j] = hi[r][j] = 0.f;
+    if (item[r] < total && mine) {
+      const T* src = qkv + (size_t)item[r] * dim;
+      Quad<T>::load(src + i0, lo[r]);
+      Quad<T>::load(src + i0 + half, hi[r]);
+    }
   }
-  const float* w = is_q ? q_norm_w : k_norm_w;
-  if (w) {
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-    if (mine) {
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {
+    const bool live = item[r] < total;        // whole groups agree, but every lane joins the shuffles
+    const int t = live ? (int)(item[r] / heads) : 0, h = live ? (int)(item[r] % heads) : 0;
+    const bool is_q = h < q_heads, is_k = !is_q && h < q_heads + kv_heads;
+    T* dst = nullptr;
+    if (live) {
+      if (is_q) {
+        dst = q_out ? q_out + ((size_t)t * q_heads + h) * dim : nullptr;   // null: a pass that only writes pages
+      } else {
+        T* pool = is_k ? k_pool : v_pool;
+        if (pool) {
+          const int kvh = is_k ? h - q_heads : h - q_heads - kv_heads;
+          const int slot = slot_map[t];
+          const size_t page = slot / page_tokens, within = slot % page_tokens;
+          dst = pool + ((page * kv_heads + kvh) * page_tokens + within) * dim;
+        } else {
+          dst = is_k ? qkv + (size_t)item[r] * dim : nullptr;              // k goes back in place, v stays
+        }
+      }
+    }
+    const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss += lo[r][j] * lo[r][j] + hi[r][j] * hi[r][j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      if (o < lanes) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!dst || !mine) continue;
+    if (w) {
+      const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        lo[j] = Elem<T>::round(w[i0 + j] * Elem<T>::round(lo[j] * inv));
-        hi[j] = Elem<T>::round(w[i0 + j + half] * Elem<T>::round(hi[j] * inv));
+        lo[r][j] = Elem<T>::round(w[i0 + j] * Elem<T>::round(lo[r][j] * inv));
+        hi[r][j] = Elem<T>::round(w[i0 + j + half] * Elem<T>::round(hi[r][j] * inv));
       }
     }
-  }
-  if (!mine) return;
-  if (inv_freq) {
-    const float pos = (float)positions[t];
+    if (rope_table && (is_q || is_k)) {
+      const float* cos_row = rope_table + ((size_t)t * 2) * n_freq;
+      const float* sin_row = cos_row + n_freq;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (i0 + j < n_freq) {
-        float sn, cs;
-        sincosf(pos * inv_freq[i0 + j], &sn, &cs);
-        const float c = Elem<T>::round(cs), s = Elem<T>::round(sn);
-        // rotate_half(x) = (-hi, lo): each product and the sum round to T
-        const float a = Elem<T>::round(Elem<T>::round(lo[j] * c) + Elem<T>::round(-hi[j] * s));
-        const float b = Elem<T>::round(Elem<T>::round(hi[j] * c) + Elem<T>::round(lo[j] * s));
-        lo[j] = a;
-        hi[j] = b;
+      for (int j = 0; j < 4; ++j) {
+        if (i0 + j < n_freq) {
+          const float c = Elem<T>::round(cos_row[i0 + j]), s = Elem<T>::round(sin_row[i0 + j]);
+          // rotate_half(x) = (-hi, lo): each product and the sum round to T
+          const float a = Elem<T>::round(Elem<T>::round(lo[r][j] * c) + Elem<T>::round(-hi[r][j] * s));
+          const float b = Elem<T>::round(Elem<T>::round(hi[r][j] * c) + Elem<T>::round(lo[r][j] * s));
+          lo[r][j] = a;
+          hi[r][j] = b;
+        }
       }
     }
+    Quad<T>::store(dst + i0, lo[r]);
+    Quad<T>::store(dst + i0 + half, hi[r]);
   }
-  Quad<T>::store(dst + i0, lo);
-  Quad<T>::store(dst + i0 + half, hi);
 }
 
 LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool, void* v_pool,
-                                 const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
-                                 const int* positions, const int* slot_map, int tokens, int q_heads, int kv_heads,
-                                 int dim, int n_freq, int page_tokens, float eps, cudaStream_t stream) {
+                                 const float* q_norm_w, const float* k_norm_w, const float* rope_table,
+                                 const int* slot_map, int tokens, int q_heads, int kv_heads, int dim, int n_freq,
+                                 int page_tokens, float eps, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dim % 8 || dim > 256 || 2 * n_freq > dim) return LB_ERR_SIZE;   // four elements of each half per lane
   // a rotation pairs i with i + dim/2 only when the rotary part spans the whole head
-  if (inv_freq && 2 * n_freq != dim) return LB_ERR_SIZE;
-  const long warps = (long)tokens * (q_heads + 2 * kv_heads);
-  const int threads = 256;
+  if (rope_table && 2 * n_freq != dim) return LB_ERR_SIZE;
+  int lanes = 1;
+  while (lanes * 8 < dim) lanes *= 2;                       // four elements of each half per lane
+  const long items = (long)tokens * (q_heads + 2 * kv_heads);
+  const long warps = (items + 2 * (32 / lanes) - 1) / (2 * (32 / lanes));
+  const int threads = 128;
   const long blocks = (warps * 32 + threads - 1) / threads;
   if (dtype == LB_F32)
     lb_launch(qk_norm_rope_kv_kernel<float>, (unsigned)blocks, threads, 0, stream, 
-        (float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, q_norm_w, k_norm_w, inv_freq, positions,
-        slot_map, tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps);
+        (float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens,
+        q_heads, kv_heads, dim, n_freq, page_tokens, eps, lanes);
   else if (dtype == LB_BF16)
     lb_launch(qk_norm_rope_kv_kernel<bf16>, (unsigned)blocks, threads, 0, stream, 
-        (bf16*)qkv, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, q_norm_w, k_norm_w, inv_freq, positions, slot_map,
-        tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps);
+        (bf16*)qkv, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
+        kv_heads, dim, n_freq, page_tokens, eps, lanes);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -430,6 +430,8 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
       if (splits < 1) splits = 1;
     }
   } else {
+    // 256-wide tiles: half the shared-memory traffic per flop of 128-wide ones, which measured
+    // slower at every size even with two blocks per SM
     bn = N > 128 ? 256 : 128;
     rows_a = M; rows_b = N;
     if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_b, W, N, K, ldw, bn)) return LB_ERR_ALIGN;

@@ -71,6 +71,7 @@ class StepBatch:
     max_ctx: int
     all_decode: bool
     real_seqs: int = 0          # entries that are not padding
+    shared: dict = field(default_factory=dict)   # what parts make once per step and share (rotary tables)
 
 
 @dataclass(frozen=True)

@@ -79,6 +79,7 @@ class Model:
     # ---- one step
     def forward(self, batch, cache) -> torch.Tensor:
         rt = self.runtime
+        batch.shared.clear()    # what parts share within a step (rotary tables) is made anew by every run
         x = torch.empty((batch.n_tokens, self.spec.hidden_size), dtype=rt.dtype, device=rt.device)
         ops.embed(batch.token_ids, self.embedding, x)
         delta = None

@@ -107,29 +107,43 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     return out
 
 
-def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor | None, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
-                    q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, inv_freq: torch.Tensor | None,
-                    positions: torch.Tensor, slot_map: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int,
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, 0, i] = cos(positions[t] * inv_freq[i]), out[t, 1, i] = sin(...); out float32 [T, 2, n_freq]."""
+    _need(positions, torch.int32, "positions"); _need(inv_freq, torch.float32, "inv_freq"); _need(out, torch.float32, "out")
+    tokens, n_freq = positions.shape[0], inv_freq.shape[0]
+    if tuple(out.shape) != (tokens, 2, n_freq):
+        raise ValueError("rope_table: out must be [tokens, 2, n_freq]")
+    fn = _fn("elementwise", "lb_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(positions), _ptr(inv_freq), _ptr(out), tokens, n_freq, _stream()), "rope_table")
+    return out
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor | None, k_pool: torch.Tensor | None,
+                    v_pool: torch.Tensor | None, q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None,
+                    table: torch.Tensor | None, slot_map: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int,
                     page_tokens: int, eps: float) -> None:
     """Per-head norm and rotation of q and k in a fused projection row, q to q_out, k and v to their pages.
 
-    qkv [T, (q_heads + 2 kv_heads) * dim]; q_out [T, q_heads * dim]; pools [pages, kv_heads, page_tokens, dim]."""
+    qkv [T, (q_heads + 2 kv_heads) * dim]; q_out [T, q_heads * dim]; pools [pages, kv_heads, page_tokens, dim];
+    table float32 [T, 2, dim / 2] from `rope_table` (None: no rotation)."""
     tokens = qkv.shape[0]
-    _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions")
+    _need(qkv, None, "qkv")
     if q_out is not None:
         _need(q_out, qkv.dtype, "q_out")
     if qkv.shape[1] != (q_heads + 2 * kv_heads) * dim:
         raise ValueError("qk_norm_rope_kv: projection row does not match the head counts")
-    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("table", table)):
         if t is not None:
             _need(t, torch.float32, name)
+    if table is not None and (table.dim() != 3 or table.shape[0] != tokens or table.shape[1] != 2):
+        raise ValueError("qk_norm_rope_kv: the rotary table must be [tokens, 2, n_freq]")
     if k_pool is not None:
         _need(k_pool, qkv.dtype, "k_pool"); _need(v_pool, qkv.dtype, "v_pool"); _need(slot_map, torch.int32, "slot_map")
-    n_freq = 0 if inv_freq is None else inv_freq.shape[0]
+    n_freq = 0 if table is None else table.shape[2]
     fn = _fn("elementwise", "lb_qk_norm_rope_kv",
-             [c_int] + [c_void_p] * 9 + [c_int] * 6 + [c_float, c_void_p])
+             [c_int] + [c_void_p] * 8 + [c_int] * 6 + [c_float, c_void_p])
     _check(fn(dtype_code(qkv.dtype), _ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w),
-              _ptr(k_norm_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_map), tokens, q_heads, kv_heads, dim, n_freq,
+              _ptr(k_norm_w), _ptr(table), _ptr(slot_map), tokens, q_heads, kv_heads, dim, n_freq,
               page_tokens, float(eps), _stream()), "qk_norm_rope_kv")
 
 

@@ -88,21 +88,21 @@ class Attention(Part):
         qkv = self.runtime.linear(h, self.w_qkv)
         q = torch.empty((tokens, self.q_heads * self.dim), dtype=h.dtype, device=h.device)
         eps = float(self.qk_norm_eps or 0.0)
-        table = self.position.inv_freq() if self.position is not None else None
+        table = self.position.tables(batch) if self.position is not None else None
         fused = self.position is None or table is not None
         k_pool, v_pool = (cache.k_pool, cache.v_pool) if own_kv else (None, None)
         if fused:
-            ops.qk_norm_rope_kv(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, batch.positions,
-                                group.slot_map, self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
+            ops.qk_norm_rope_kv(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, group.slot_map,
+                                self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
         else:
             # norm in place, the position encoding as its own step, then the page write
-            ops.qk_norm_rope_kv(qkv, q, None, None, self.q_norm_w, self.k_norm_w, None, batch.positions, None,
+            ops.qk_norm_rope_kv(qkv, q, None, None, self.q_norm_w, self.k_norm_w, None, None,
                                 self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
             k_rows = qkv[:, self.q_heads * self.dim:(self.q_heads + own_kv) * self.dim]
             self.position.apply(q.view(tokens, self.q_heads, self.dim),
                                 k_rows.unflatten(1, (own_kv, self.dim)) if own_kv else None, batch.positions)
             if own_kv:
-                ops.qk_norm_rope_kv(qkv, None, k_pool, v_pool, None, None, None, batch.positions, group.slot_map,
+                ops.qk_norm_rope_kv(qkv, None, k_pool, v_pool, None, None, None, group.slot_map,
                                     self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
         out = torch.empty_like(q)
         self.attend(q, cache, batch, group, out)

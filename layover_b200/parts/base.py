@@ -12,8 +12,9 @@ What each kind must offer:
                   bind(tensors, runtime)              take them (fuse or reshape as it likes)
   norm            forward(x, delta, rows=None) -> h   x += delta in place (delta may be None), h = norm(x);
                                                       with rows, only those rows, x untouched
-  position        inv_freq(device) -> float32 table or None   when the fused rotation kernel can apply it
-                  apply(q, k, positions)              otherwise: rotate q [T, heads, dim], k in place
+  position        tables(batch) -> float32 [T, 2, dim/2] cos/sin of the step, or None; made once per
+                                                      step and kept in batch.shared (the fused kernel applies it)
+                  apply(q, k, positions)              when tables() is None: rotate q [T, heads, dim], k in place
   mixer           cache_need() -> PagedKVNeed | StateNeed | None
                   forward(h, batch, cache) -> [T, hidden]     cache is the view it was given for its need
   feed-forward    forward(h) -> [T, hidden]

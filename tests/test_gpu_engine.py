@@ -153,6 +153,12 @@ def test_position_part_alone():
     rope.bind({}, runtime(torch.float32))
     expected = 1.0 / (12345.0 ** (torch.arange(0, 48, 2, dtype=torch.float32) / 48))
     assert torch.equal(rope.inv_freq().cpu(), expected)
+    from types import SimpleNamespace
+    batch = SimpleNamespace(n_tokens=3, positions=torch.tensor([0, 7, 300], dtype=torch.int32, device="cuda"), shared={})
+    table = rope.tables(batch)
+    angles = torch.tensor([0.0, 7.0, 300.0])[:, None] * expected[None, :]
+    assert (table[:, 0].cpu() - angles.cos()).abs().max() < 1e-5 and (table[:, 1].cpu() - angles.sin()).abs().max() < 1e-5
+    assert rope.tables(batch) is table               # made once per step, then shared
     with pytest.raises(ValueError, match="unknown position kind"):
         build_part("position", PartSpec("alibi", {}), "")
 

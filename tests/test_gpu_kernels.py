@@ -221,8 +221,10 @@ def test_qk_norm_rope_kv(dtype, q_heads, kv_heads, dim, page):
     v_pool = torch.zeros_like(k_pool)
     q_out = torch.empty(tokens, q_heads * dim, dtype=dtype, device="cuda")
     inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).cuda()
-    o.qk_norm_rope_kv(qkv.cuda(), q_out, k_pool, v_pool, qn.float().cuda(), kn.float().cuda(), inv_freq,
-                      positions.cuda(), slots.cuda(), q_heads, kv_heads, dim, page, eps)
+    table = torch.empty(tokens, 2, dim // 2, device="cuda")
+    o.rope_table(positions.cuda(), inv_freq, table)
+    o.qk_norm_rope_kv(qkv.cuda(), q_out, k_pool, v_pool, qn.float().cuda(), kn.float().cuda(), table,
+                      slots.cuda(), q_heads, kv_heads, dim, page, eps)
     heads = qkv.view(tokens, q_heads + 2 * kv_heads, dim)
     cos, sin = plain_rope_tables(positions, dim, theta, dtype)
     q_ref = plain_apply_rope(plain_rmsnorm(heads[:, :q_heads], qn, eps), cos, sin)
@@ -248,7 +250,11 @@ def test_qk_norm_rope_small_positions_are_tight():
     inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).cuda()
     q_out = torch.empty(4, dim, device="cuda")
     k_pool = torch.zeros(1, 1, 4, dim, device="cuda"); v_pool = torch.zeros_like(k_pool)
-    o.qk_norm_rope_kv(x.cuda(), q_out, k_pool, v_pool, None, None, inv_freq, positions.cuda(),
+    table = torch.empty(4, 2, dim // 2, device="cuda")
+    o.rope_table(positions.cuda(), inv_freq, table)
+    angles = positions.float()[:, None] * inv_freq.cpu()[None, :]
+    assert (table[:, 0].cpu() - angles.cos()).abs().max() < 2e-6 and (table[:, 1].cpu() - angles.sin()).abs().max() < 2e-6
+    o.qk_norm_rope_kv(x.cuda(), q_out, k_pool, v_pool, None, None, table,
                       torch.arange(4, dtype=torch.int32, device="cuda"), 1, 1, dim, 4, 0.0)
     cos, sin = plain_rope_tables(positions, dim, theta, torch.float32)
     expected = plain_apply_rope(x.view(4, 3, dim)[:, :1], cos, sin)
@@ -259,8 +265,7 @@ def test_refused_sizes_raise_instead_of_computing():
     o = ops()
     x = torch.zeros(2, 3 * 258, device="cuda")
     with pytest.raises(ValueError, match="unsupported size"):
-        o.qk_norm_rope_kv(x, torch.zeros(2, 258, device="cuda"), None, None, None, None, None,
-                          torch.zeros(2, dtype=torch.int32, device="cuda"), None, 1, 1, 258, 4, 0.0)
+        o.qk_norm_rope_kv(x, torch.zeros(2, 258, device="cuda"), None, None, None, None, None, None, 1, 1, 258, 4, 0.0)
     with pytest.raises(ValueError, match="contiguous"):
         o.swiglu(torch.zeros(4, 8, device="cuda").t(), torch.zeros(8, 2, device="cuda"))
     with pytest.raises(Exception, match="CUDA"):
