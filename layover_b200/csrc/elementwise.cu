@@ -234,16 +234,22 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
   const bool mine = i0 < half;
 
   long item[ROUNDS];
-  float lo[ROUNDS][4], hi[ROUNDS][4];
+  float lo[ROUNDS][4], hi[ROUNDS][4], cs[ROUNDS][4], sn[ROUNDS][4];
+  const bool rotate = rope_table && i0 + 4 <= n_freq;    // n_freq = half whenever a table is given
 #pragma unroll
   for (int r = 0; r < ROUNDS; ++r) {
     item[r] = (warp * ROUNDS + r) * per_warp + sub;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) lo[r][j] = hi[r][j] = 0.f;
+    for (int j = 0; j < 4; ++j) { lo[r][j] = hi[r][j] = 0.f; cs[r][j] = 1.f; sn[r][j] = 0.f; }
     if (item[r] < total && mine) {
       const T* src = qkv + (size_t)item[r] * dim;
       Quad<T>::load(src + i0, lo[r]);
       Quad<T>::load(src + i0 + half, hi[r]);
+      if (rotate) {     // the table's values travel with the data, not after the reduction
+        const float* cos_row = rope_table + ((size_t)(item[r] / heads) * 2) * n_freq + i0;
+        Pack<float>::load(cos_row, cs[r]);
+        Pack<float>::load(cos_row + n_freq, sn[r]);
+      }
     }
   }
 #pragma unroll
@@ -283,13 +289,11 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
         hi[r][j] = Elem<T>::round(w[i0 + j + half] * Elem<T>::round(hi[r][j] * inv));
       }
     }
-    if (rope_table && (is_q || is_k)) {
-      const float* cos_row = rope_table + ((size_t)t * 2) * n_freq;
-      const float* sin_row = cos_row + n_freq;
+    if (rotate && (is_q || is_k)) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        if (i0 + j < n_freq) {
-          const float c = Elem<T>::round(cos_row[i0 + j]), s = Elem<T>::round(sin_row[i0 + j]);
+        {
+          const float c = Elem<T>::round(cs[r][j]), s = Elem<T>::round(sn[r][j]);
           // rotate_half(x) = (-hi, lo): each product and the sum round to T
           const float a = Elem<T>::round(Elem<T>::round(lo[r][j] * c) + Elem<T>::round(-hi[r][j] * s));
           const float b = Elem<T>::round(Elem<T>::round(hi[r][j] * c) + Elem<T>::round(lo[r][j] * s));

@@ -10,15 +10,22 @@
 //                          the N side, so the tensor core's 128 rows are always full and the
 //                          kernel is a pure stream of the weight matrix. When the weight has too
 //                          few 128-row tiles to occupy the GPU, K is split over several blocks;
-//                          each writes a 32-bit partial tile to scratch memory and the block that
-//                          arrives last adds them in split order (a fixed order, so the result
-//                          does not depend on timing) and resets the tile's counter.
+//                          each writes a 32-bit partial tile to scratch memory and then adds up
+//                          its share of the tile's columns over all splits in split order (a
+//                          fixed order, so the result does not depend on timing).
 //
-// Block = 4 warps. Warp 0 lane 0 issues TMA loads through a ring of stages, warp 1 lane 0 issues
-// the MMAs and frees stages with tcgen05.commit; all four warps run the epilogue (warp w owns
-// tensor-memory lanes 32w..32w+31). Every wait on an mbarrier is bounded: when a limit runs out
-// the block records an error code, lets copies in flight land, frees its tensor memory and
-// returns; `lb_gemm_tcgen05_status` reports it.
+// Two kernels share the PTX wrappers, descriptors and epilogue stores:
+//   many tokens: persistent blocks of six warps, one per SM. Warp 0 lane 0 issues TMA loads through
+//     a ring of stages, warp 1 lane 0 issues the MMAs into one of two accumulators in tensor memory
+//     and frees stages with tcgen05.commit, warps 2-5 run the epilogue of the other accumulator.
+//     Whole rounds of tiles are dealt one tile per block; the tiles left over are split along K so
+//     that the last round keeps every SM busy, and the blocks of a tile then add up the partial
+//     tiles together, each its share of the columns, in split order.
+//   few tokens: one tile (or one K range of a tile) per block of four warps, two blocks per SM; the
+//     block that arrives last at the tile's counter adds the partial tiles in split order.
+// Every wait (on an mbarrier, or on sibling blocks) is bounded: when a limit runs out the block
+// records an error code, lets copies in flight land, frees its tensor memory and returns;
+// `lb_gemm_tcgen05_status` reports it.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -29,11 +36,10 @@ namespace {
 constexpr int BM = 128;          // rows of the MMA's M side
 constexpr int BK = 64;           // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 128;
 constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-__device__ int g_gemm_error = 0;   // 0 = ok; 1 producer, 2 mma, 3 epilogue wait ran out
+__device__ int g_gemm_error = 0;   // 0 = ok; a wait ran out in 1 the producer, 2 the MMA issuer, 3 the epilogue, 4 the split sum
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -133,26 +139,34 @@ template <> __device__ __forceinline__ void store_row16<bf16>(bf16* p, const flo
   reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
+// Persistent blocks, each over its share of the work. Shared memory holds a ring of stages
+// (one 128 x 64 tile of the 128-row operand and one BN x 64 tile of the other); tensor memory holds
+// two accumulators, so the epilogue of one tile overlaps the MMAs of the next.
+constexpr int SMALL_THREADS = 128;
+
 // The few-token orientation keeps two blocks on an SM (half the shared memory each), so that a
 // weight matrix with about as many tiles as SMs, or one split in two, still runs in one wave.
-template <int BN, bool SWAP> struct Tile {
+template <int BN> struct SmallTile {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BUDGET = SWAP ? SMEM_BUDGET / 2 : SMEM_BUDGET;
+  static constexpr int BUDGET = SMEM_BUDGET / 2;
   static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
-  static constexpr int BLOCKS_PER_SM = SWAP ? 2 : 1;
+  static constexpr int BLOCKS_PER_SM = 2;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-// D[i, j] = sum_k Aop[i, k] Bop[j, k], i on the 128-row side. SWAP false: C[i, j] = D; true: C[j, i] = D.
-template <int BN, bool SWAP, typename OutT>
-__global__ void __launch_bounds__(THREADS, Tile<BN, SWAP>::BLOCKS_PER_SM)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+// The few-token kernel: D[i, j] = sum_k W[i, k] X[j, k] with 128 weight rows i per block, C[j, i] = D.
+// One tile (or one K range of a tile) per block, two blocks per SM, four warps that all join the
+// epilogue: for these short streams it starts and ends a few microseconds sooner than the
+// persistent kernel below.
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(SMALL_THREADS, SmallTile<BN>::BLOCKS_PER_SM)
+gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, int K, int splits,
                     float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok) {
-  using T = Tile<BN, SWAP>;
+  using T = SmallTile<BN>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles_a = smem;
@@ -189,13 +203,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int early = n_kb < T::STAGES ? n_kb : T::STAGES;
     for (int i = 0; i < early; ++i) {
       mbar_expect_tx(&full[i], T::STAGE_BYTES);
-      if (SWAP) tma_load_2d(tiles_a + i * T::A_BYTES, &map_a, &full[i], (kb_begin + i) * BK, m0);
-      else tma_load_2d(tiles_b + i * T::B_BYTES, &map_b, &full[i], (kb_begin + i) * BK, n0);
+      tma_load_2d(tiles_a + i * T::A_BYTES, &map_a, &full[i], (kb_begin + i) * BK, m0);
     }
     pdl_wait();
     for (int i = 0; i < early; ++i) {
-      if (SWAP) tma_load_2d(tiles_b + i * T::B_BYTES, &map_b, &full[i], (kb_begin + i) * BK, n0);
-      else tma_load_2d(tiles_a + i * T::A_BYTES, &map_a, &full[i], (kb_begin + i) * BK, m0);
+      tma_load_2d(tiles_b + i * T::B_BYTES, &map_b, &full[i], (kb_begin + i) * BK, n0);
     }
     for (int i = early; i < n_kb; ++i) {
       const int s = i % T::STAGES;
@@ -244,7 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           if (c + i < valid_cols) my_partial[(size_t)(c + i) * BM + row] = v[i];
-      } else if (SWAP) {
+      } else if (true) {
         if (m0 + row < rows_a) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
@@ -301,13 +313,329 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             if (j0 + u < valid_cols) {
-              if (SWAP) store_one<OutT>(C + (size_t)(n0 + j0 + u) * ldc + m0 + row, sum[u]);
+              if (true) store_one<OutT>(C + (size_t)(n0 + j0 + u) * ldc + m0 + row, sum[u]);
               else store_one<OutT>(C + (size_t)(m0 + row) * ldc + n0 + j0 + u, sum[u]);
             }
           }
         }
       }
       if (threadIdx.x == 0) counters[tile_id] = 0;   // ready for the next launch
+    }
+  }
+
+  // ---------------- teardown
+  fence_before_sync();
+  __syncthreads();
+  if (flag[0]) {
+    // a wait ran out: give copies still in flight time to land before the block's memory goes away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------ the persistent kernel
+// The few-token orientation asks for two blocks per SM (half the shared memory each): a weight
+// matrix with about as many tiles as SMs then still runs in one round.
+template <int BN, bool SWAP> struct Tile {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BLOCKS_PER_SM = SWAP ? 2 : 1;
+  static constexpr int BUDGET = SMEM_BUDGET / BLOCKS_PER_SM;
+  static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
+  static constexpr int ACC_COLS = BN < 16 ? 16 : BN;          // columns of one accumulator
+  static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// How the output tiles are dealt to the blocks. Tiles are numbered with the 128-row side fastest.
+// `full` rounds give block b the whole tile round * blocks + b. The `rem` tiles left over form a
+// last round in which each tile is cut into `last_splits` ranges of K, one per block; a block
+// whose range is not the whole K writes a 32-bit partial tile to scratch memory and the block that
+// has a partial tile then adds up its own share of the tile's columns, in split order.
+struct Schedule {
+  int tiles_m, tiles, full, rem, last_splits, total_kb;
+};
+
+struct Segment {
+  int tile, split, splits, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ int segment_count(const Schedule& sch, int block) {
+  return sch.full + ((sch.rem > 0 && block < sch.rem * sch.last_splits) ? 1 : 0);
+}
+__device__ __forceinline__ Segment segment_at(const Schedule& sch, int block, int blocks, int j) {
+  Segment seg;
+  if (j < sch.full) {
+    seg.tile = j * blocks + block; seg.split = 0; seg.splits = 1; seg.kb_begin = 0; seg.kb_end = sch.total_kb;
+  } else {
+    seg.tile = sch.full * blocks + block % sch.rem;
+    seg.split = block / sch.rem;
+    seg.splits = sch.last_splits;
+    seg.kb_begin = (int)((long)sch.total_kb * seg.split / seg.splits);
+    seg.kb_end = (int)((long)sch.total_kb * (seg.split + 1) / seg.splits);
+  }
+  return seg;
+}
+
+constexpr int EPILOGUE_WARPS = 4;
+constexpr int PERSISTENT_THREADS = (2 + EPILOGUE_WARPS) * 32;
+
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// D[i, j] = sum_k Aop[i, k] Bop[j, k], i on the 128-row side. SWAP false: C[i, j] = D; true: C[j, i] = D.
+template <int BN, bool SWAP, typename OutT>
+__global__ void __launch_bounds__(PERSISTENT_THREADS, Tile<BN, SWAP>::BLOCKS_PER_SM)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    OutT* __restrict__ C, long ldc, int rows_a, int rows_b, const Schedule sch,
+                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok) {
+  using T = Tile<BN, SWAP>;
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles_a = smem;
+  uint8_t* tiles_b = smem + T::STAGES * T::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + T::STAGES * T::STAGE_BYTES);
+  uint64_t* empty = full + T::STAGES;
+  uint64_t* acc_full = empty + T::STAGES;     // [2] the MMAs of an accumulator are done
+  uint64_t* acc_empty = acc_full + 2;         // [2] the epilogue has read an accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* flag = tmem_slot + 1;    // [0] a wait ran out, [1] this block is the last of its tile
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int block = blockIdx.x, blocks = gridDim.x;
+  const int n_segments = segment_count(sch, block);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPILOGUE_WARPS); }
+    flag[0] = 0; flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, T::TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer. Weights are written by no kernel, so the first ring of weight
+      // tiles is requested before waiting for the kernel that produces the activations.
+      int it = 0;                       // K blocks issued so far, over all segments
+      bool waited = false;
+      for (int j = 0; j < n_segments && !flag[0]; ++j) {
+        const Segment seg = segment_at(sch, block, blocks, j);
+        const int m0 = (seg.tile % sch.tiles_m) * BM, n0 = (seg.tile / sch.tiles_m) * BN;
+        for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
+          const int s = it % T::STAGES;
+          const uint32_t phase = (it / T::STAGES) & 1;
+          if (it >= T::STAGES && !waited) {
+            // the ring is full of weight tiles: now the activations are needed
+            pdl_wait();
+            waited = true;
+            int back = 0;               // replay the first ring's activation tiles
+            for (int jj = 0; jj <= j && back < T::STAGES; ++jj) {
+              const Segment early = segment_at(sch, block, blocks, jj);
+              const int em0 = (early.tile % sch.tiles_m) * BM, en0 = (early.tile / sch.tiles_m) * BN;
+              for (int ekb = early.kb_begin; ekb < early.kb_end && back < T::STAGES; ++ekb, ++back) {
+                if (SWAP) tma_load_2d(tiles_b + back * T::B_BYTES, &map_b, &full[back], ekb * BK, en0);
+                else tma_load_2d(tiles_a + back * T::A_BYTES, &map_a, &full[back], ekb * BK, em0);
+              }
+            }
+          }
+          if (it >= T::STAGES && !mbar_wait(&empty[s], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 1); flag[0] = 1; break; }
+          mbar_expect_tx(&full[s], T::STAGE_BYTES);
+          if (!waited) {                // only the weight half for now
+            if (SWAP) tma_load_2d(tiles_a + s * T::A_BYTES, &map_a, &full[s], kb * BK, m0);
+            else tma_load_2d(tiles_b + s * T::B_BYTES, &map_b, &full[s], kb * BK, n0);
+          } else {
+            tma_load_2d(tiles_a + s * T::A_BYTES, &map_a, &full[s], kb * BK, m0);
+            tma_load_2d(tiles_b + s * T::B_BYTES, &map_b, &full[s], kb * BK, n0);
+          }
+        }
+      }
+      if (!waited) {                    // fewer K blocks than stages: same replay, after the wait
+        pdl_wait();
+        int back = 0;
+        for (int jj = 0; jj < n_segments && back < T::STAGES; ++jj) {
+          const Segment early = segment_at(sch, block, blocks, jj);
+          const int em0 = (early.tile % sch.tiles_m) * BM, en0 = (early.tile / sch.tiles_m) * BN;
+          for (int ekb = early.kb_begin; ekb < early.kb_end && back < T::STAGES; ++ekb, ++back) {
+            if (SWAP) tma_load_2d(tiles_b + back * T::B_BYTES, &map_b, &full[back], ekb * BK, en0);
+            else tma_load_2d(tiles_a + back * T::A_BYTES, &map_a, &full[back], ekb * BK, em0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      constexpr uint32_t idesc = instr_desc(BN);
+      int it = 0;
+      for (int j = 0; j < n_segments && !flag[0]; ++j) {
+        const Segment seg = segment_at(sch, block, blocks, j);
+        const int buf = j & 1;
+        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, 2); flag[0] = 1; break; }
+        fence_after_sync();
+        const uint32_t acc = tmem_base + buf * T::ACC_COLS;
+        for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
+          const int s = it % T::STAGES;
+          const uint32_t phase = (it / T::STAGES) & 1;
+          if (!mbar_wait(&full[s], phase)) { atomicCAS(&g_gemm_error, 0, 2); flag[0] = 1; break; }
+          fence_after_sync();
+          const uint64_t a_desc = smem_desc(tiles_a + s * T::A_BYTES), b_desc = smem_desc(tiles_b + s * T::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)   // +32 bytes per K step inside the swizzled row
+            umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > seg.kb_begin || k > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        if (flag[0]) break;
+        umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ---------------- epilogue: four warps, each owning the accumulator lanes 32 (warp % 4) ..
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                    // row of the 128-row side
+    pdl_wait();   // the stores below touch memory that earlier kernels may still be reading
+    for (int j = 0; j < n_segments; ++j) {
+      const Segment seg = segment_at(sch, block, blocks, j);
+      const int m0 = (seg.tile % sch.tiles_m) * BM, n0 = (seg.tile / sch.tiles_m) * BN;
+      const int buf = j & 1;
+      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1)) { atomicCAS(&g_gemm_error, 0, 3); flag[0] = 1; break; }
+      fence_after_sync();
+      const uint32_t lane_base = tmem_base + buf * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      const int valid_cols = min(BN, rows_b - n0);
+      const int slot = seg.tile - sch.full * blocks;         // index among the last round's tiles
+      float* my_partial = seg.splits > 1 ? partials + ((size_t)slot * seg.splits + seg.split) * BN * BM : nullptr;
+      for (int c = 0; c < BN; c += 16) {
+        if (c >= valid_cols) break;                           // uniform over the block
+        float v[16];
+        tmem_ld16(lane_base + c, v);
+        if (seg.splits > 1) {
+          // four columns of a row side by side: 16-byte stores here, 16-byte loads in the sum
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            reinterpret_cast<float4*>(my_partial)[(size_t)((c >> 2) + i) * BM + row] =
+                make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else if (SWAP) {
+          if (m0 + row < rows_a) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (c + i < valid_cols) store_one<OutT>(C + (size_t)(n0 + c + i) * ldc + m0 + row, v[i]);
+          }
+        } else {
+          if (m0 + row < rows_a) {
+            OutT* dst = C + (size_t)(m0 + row) * ldc + n0 + c;
+            if (vector_ok && c + 16 <= valid_cols) {
+              store_row16<OutT>(dst, v);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (c + i < valid_cols) store_one<OutT>(dst + i, v[i]);
+            }
+          }
+        }
+      }
+      // the accumulator may be overwritten now
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+
+      if (seg.splits > 1) {
+        // Every block of the tile adds up its own share of the columns, over all splits in split
+        // order, once all partial tiles are there. All blocks of a launch are resident at once
+        // (one per SM, at most as many as SMs), so waiting for the siblings is safe; the wait is
+        // bounded all the same. counters[2 slot] counts partial tiles written, [2 slot + 1] counts
+        // blocks that finished reading; the last reader puts both back to zero.
+        volatile unsigned* written = counters + 2 * slot;
+        __threadfence();
+        epilogue_sync();
+        if (threadIdx.x == 64) {
+          atomicAdd(const_cast<unsigned*>(written), 1u);
+          bool ok = false;
+          for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+            if (*written >= (unsigned)seg.splits) { ok = true; break; }
+            __nanosleep(32);
+          }
+          if (!ok) { atomicCAS(&g_gemm_error, 0, 4); flag[0] = 1; }
+          flag[1] = ok ? 1u : 0u;
+        }
+        epilogue_sync();
+        if (flag[1]) {
+          __threadfence();
+          const float4* tile_partials = reinterpret_cast<const float4*>(partials + (size_t)slot * seg.splits * BN * BM);
+          const int quads = (valid_cols + 3) >> 2;                      // groups of four columns
+          const int share = (quads + seg.splits - 1) / seg.splits;
+          const int q_begin = seg.split * share, q_end = min(quads, q_begin + share);
+          if (m0 + row < rows_a) {
+            for (int q0 = q_begin; q0 < q_end; q0 += 4) {
+              float4 sum[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s0 = 0; s0 < seg.splits; s0 += 4) {
+                float4 part[4][4];
+#pragma unroll
+                for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+                  for (int u = 0; u < 4; ++u)
+                    part[ds][u] = (s0 + ds < seg.splits && q0 + u < q_end)
+                                      ? tile_partials[((size_t)(s0 + ds) * (BN / 4) + q0 + u) * BM + row]
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    sum[u].x += part[ds][u].x; sum[u].y += part[ds][u].y;
+                    sum[u].z += part[ds][u].z; sum[u].w += part[ds][u].w;
+                  }
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (q0 + u >= q_end) continue;
+                const int col = (q0 + u) * 4;
+                const float vals[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+                if (!SWAP && vector_ok && col + 4 <= valid_cols) {
+                  OutT* dst = C + (size_t)(m0 + row) * ldc + n0 + col;
+                  if (sizeof(OutT) == 2) {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(vals[0], vals[1]), hi = __floats2bfloat162_rn(vals[2], vals[3]);
+                    uint2 w;
+                    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+                    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst) = w;
+                  } else {
+                    *reinterpret_cast<float4*>(dst) = sum[u];
+                  }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (col + e < valid_cols) {
+                      if (SWAP) store_one<OutT>(C + (size_t)(n0 + col + e) * ldc + m0 + row, vals[e]);
+                      else store_one<OutT>(C + (size_t)(m0 + row) * ldc + n0 + col + e, vals[e]);
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+        epilogue_sync();
+        if (threadIdx.x == 64 && flag[1]) {
+          const unsigned finished = atomicAdd(counters + 2 * slot + 1, 1u);
+          if (finished == (unsigned)seg.splits - 1) {   // everyone has read: ready for the next launch
+            counters[2 * slot + 1] = 0;
+            __threadfence();
+            *written = 0;
+          }
+        }
+      }
     }
   }
 
@@ -351,34 +679,107 @@ bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, in
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// What the caller knows about the product; the launcher turns it into a schedule.
+struct Problem {
+  int rows_a, rows_b, K, bn;
+  bool swap;
+  int sm_count, max_splits;
+  float* scratch;
+  long scratch_floats;
+  unsigned* counters;
+  int n_counters;
+};
+
 template <int BN, bool SWAP, typename OutT>
-int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, int rows_a, int rows_b, int K,
-           int splits, float* partials, unsigned* counters, bool vector_ok, cudaStream_t stream) {
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb, bool vector_ok,
+           cudaStream_t stream) {
   using T = Tile<BN, SWAP>;
   auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT>;
+  static int blocks_per_sm = 0;      // how many blocks of this kernel an SM really holds
+  if (blocks_per_sm == 0) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
+      return lb_last_error();
+    int fit = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, kernel, PERSISTENT_THREADS, T::SMEM) != cudaSuccess || fit < 1)
+      return lb_last_error() ? lb_last_error() : LB_ERR_SIZE;
+    blocks_per_sm = fit < T::BLOCKS_PER_SM ? fit : T::BLOCKS_PER_SM;
+  }
+  // Blocks that split a tile wait for one another, so a launch never has more blocks than the GPU
+  // holds at once.
+  const int slots = pb.sm_count * blocks_per_sm;
+  Schedule sch;
+  sch.tiles_m = (pb.rows_a + BM - 1) / BM;
+  sch.tiles = sch.tiles_m * ((pb.rows_b + BN - 1) / BN);
+  sch.total_kb = (pb.K + BK - 1) / BK;
+  // A split costs a partial tile to write, a fence, a counter and a longer sum; wider token tiles
+  // make the partial tiles bigger. Measured on 2560..9728-wide weights: 8 splits of a 20-tile
+  // matrix beat 15, and 128-token tiles want 2. One block per SM streams a weight matrix at close
+  // to full bandwidth, so splitting aims at one block per SM, not at every slot.
+  int cap = SWAP ? (BN <= 16 ? 8 : (BN <= 32 ? 4 : 2)) : 4;
+  if (pb.max_splits > 0 && cap > pb.max_splits) cap = pb.max_splits;
+  if (!pb.scratch || !pb.counters) cap = 1;
+  int blocks;
+  if (sch.tiles >= slots) {
+    blocks = slots;
+    sch.full = sch.tiles / blocks;
+    sch.rem = sch.tiles % blocks;
+  } else {
+    blocks = sch.tiles;              // grows below when the tiles are split
+    sch.full = 0;
+    sch.rem = sch.tiles;
+  }
+  sch.last_splits = 1;
+  if (sch.rem > 0) {
+    int splits = sch.rem < pb.sm_count ? (pb.sm_count + sch.rem - 1) / sch.rem : 1;
+    if (splits > cap) splits = cap;
+    if (splits > sch.total_kb / 4) splits = sch.total_kb / 4;       // at least four K blocks per split
+    if (splits > slots / sch.rem) splits = slots / sch.rem;
+    const long per_split = (long)sch.rem * BN * BM;
+    if (splits > 1 && per_split * splits > pb.scratch_floats) splits = (int)(pb.scratch_floats / per_split);
+    if (splits > 1 && 2 * sch.rem > pb.n_counters) splits = 1;
+    if (splits < 1) splits = 1;
+    sch.last_splits = splits;
+    if (sch.full == 0) blocks = sch.rem * splits;
+  }
+  float* partials = sch.last_splits > 1 ? pb.scratch : nullptr;
+  const int code = lb_launch(kernel, dim3(blocks), dim3(PERSISTENT_THREADS), (size_t)T::SMEM, stream, map_a, map_b,
+                             (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials, pb.counters, vector_ok);
+  return code ? code : lb_last_error();
+}
+
+template <int BN, typename OutT>
+int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb,
+                    cudaStream_t stream) {
+  using T = SmallTile<BN>;
+  auto kernel = gemm_fewtoken_kernel<BN, OutT>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
       return lb_last_error();
     configured = true;
   }
-  dim3 grid((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, splits);
-  const int code = lb_launch(kernel, grid, dim3(THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc, rows_a,
-                             rows_b, K, splits, partials, counters, vector_ok);
-  return code ? code : lb_last_error();
-}
-
-template <bool SWAP, typename OutT>
-int launch_bn(int bn, const CUtensorMap& a, const CUtensorMap& b, void* C, long ldc, int rows_a, int rows_b, int K,
-              int splits, float* partials, unsigned* counters, bool vector_ok, cudaStream_t stream) {
-  switch (bn) {
-    case 16: return launch<16, SWAP, OutT>(a, b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
-    case 32: return launch<32, SWAP, OutT>(a, b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
-    case 64: return launch<64, SWAP, OutT>(a, b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
-    case 128: return launch<128, SWAP, OutT>(a, b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
-    case 256: return launch<256, SWAP, OutT>(a, b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
+  const int tiles = (pb.rows_a + BM - 1) / BM, total_kb = (pb.K + BK - 1) / BK;
+  int splits = 1;
+  if (pb.scratch && pb.counters && tiles <= pb.n_counters && tiles < pb.sm_count) {
+    // One block per SM streams a weight matrix at close to full bandwidth, and every further
+    // split adds a partial tile to write, a fence, a counter and a longer sum, which at these
+    // sizes cost more than the extra blocks win (measured on 2560..9728-wide weights: 8 splits
+    // of a 20-tile matrix beat 15; a 152-tile matrix is fastest unsplit). Wider token tiles
+    // make the partial tiles bigger, so they split less.
+    const int cap = BN <= 16 ? 8 : (BN <= 32 ? 4 : 2);
+    splits = (pb.sm_count + tiles - 1) / tiles;
+    if (splits > cap) splits = cap;
+    if (splits > total_kb / 4) splits = total_kb / 4;         // at least four K blocks per split
+    if (pb.max_splits > 0 && splits > pb.max_splits) splits = pb.max_splits;
+    const long per_split = (long)tiles * BN * BM;
+    if (splits > 1 && per_split * splits > pb.scratch_floats) splits = (int)(pb.scratch_floats / per_split);
+    if (splits < 1) splits = 1;
   }
-  return LB_ERR_SIZE;
+  dim3 grid(tiles, (pb.rows_b + BN - 1) / BN, splits);
+  const int code = lb_launch(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc,
+                             pb.rows_a, pb.rows_b, pb.K, splits, splits > 1 ? pb.scratch : (float*)nullptr, pb.counters,
+                             false);
+  return code ? code : lb_last_error();
 }
 }  // namespace
 
@@ -398,37 +799,21 @@ LB_EXPORT int lb_gemm_tcgen05_supports(const void* A, const void* W, int K, long
 
 // C[M, N] = A[M, K] W[N, K]^T. out_dtype: LB_BF16 or LB_F32. `scratch` (floats) and `counters`
 // (zeroed once by the caller, `n_counters` of them) serve the split-K path; without them K is
-// never split. `sm_count` sizes the split; `max_splits` > 0 caps it.
+// never split. `sm_count` sizes the grid; `max_splits` > 0 caps the splitting.
 LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K, long lda,
                               long ldw, long ldc, float* scratch, long scratch_floats, unsigned* counters,
                               int n_counters, int sm_count, int max_splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lb_gemm_tcgen05_supports(A, W, K, lda, ldw)) return LB_ERR_ALIGN;
   if (out_dtype != LB_BF16 && out_dtype != LB_F32) return LB_ERR_DTYPE;
+  if (sm_count < 1) sm_count = 1;
   const bool swap = M <= 128;
   CUtensorMap map_a, map_b;
-  int bn, rows_a, rows_b, splits = 1;
+  int bn, rows_a, rows_b;
   if (swap) {
     bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     rows_a = N; rows_b = M;
     if (!make_map(&map_a, W, N, K, ldw, BM) || !make_map(&map_b, A, M, K, lda, bn)) return LB_ERR_ALIGN;
-    const int tiles = (N + BM - 1) / BM;
-    const int total_kb = (K + BK - 1) / BK;
-    if (scratch && counters && tiles <= n_counters && tiles < sm_count) {
-      // One block per SM streams a weight matrix at close to full bandwidth, and every further
-      // split adds a partial tile to write, a fence, a counter and a longer sum, which at these
-      // sizes cost more than the extra blocks win (measured on 2560..9728-wide weights: 8 splits
-      // of a 20-tile matrix beat 15; a 152-tile matrix is fastest unsplit). Wider token tiles
-      // make the partial tiles bigger, so they split less.
-      const int cap = bn <= 16 ? 8 : (bn <= 32 ? 4 : 2);
-      splits = (sm_count + tiles - 1) / tiles;
-      if (splits > cap) splits = cap;
-      if (splits > total_kb / 4) splits = total_kb / 4;         // at least four K blocks per split
-      if (max_splits > 0 && splits > max_splits) splits = max_splits;
-      const long per_split = (long)tiles * bn * BM;
-      if (splits > 1 && per_split * splits > scratch_floats) splits = (int)(scratch_floats / per_split);
-      if (splits < 1) splits = 1;
-    }
   } else {
     // 256-wide tiles: half the shared-memory traffic per flop of 128-wide ones, which measured
     // slower at every size even with two blocks per SM
@@ -436,15 +821,26 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
     rows_a = M; rows_b = N;
     if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_b, W, N, K, ldw, bn)) return LB_ERR_ALIGN;
   }
-  float* partials = splits > 1 ? scratch : nullptr;
+  const Problem pb{rows_a, rows_b, K, bn, swap, sm_count, max_splits, scratch, scratch_floats, counters, n_counters};
   const int elem = out_dtype == LB_BF16 ? 2 : 4;
   const bool vector_ok = ((uintptr_t)C % 16 == 0) && ((ldc * elem) % 16 == 0);
-  if (swap) {
-    if (out_dtype == LB_BF16)
-      return launch_bn<true, bf16>(bn, map_a, map_b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
-    return launch_bn<true, float>(bn, map_a, map_b, C, ldc, rows_a, rows_b, K, splits, partials, counters, vector_ok, stream);
+#define LB_GEMM_CASE(BN_, SWAP_)                                                                       \
+  if (bn == BN_ && swap == SWAP_) {                                                                    \
+    if (out_dtype == LB_BF16) return launch<BN_, SWAP_, bf16>(map_a, map_b, C, ldc, pb, vector_ok, stream); \
+    return launch<BN_, SWAP_, float>(map_a, map_b, C, ldc, pb, vector_ok, stream);                     \
   }
-  if (out_dtype == LB_BF16)
-    return launch_bn<false, bf16>(bn, map_a, map_b, C, ldc, rows_a, rows_b, K, 1, nullptr, nullptr, vector_ok, stream);
-  return launch_bn<false, float>(bn, map_a, map_b, C, ldc, rows_a, rows_b, K, 1, nullptr, nullptr, vector_ok, stream);
+#define LB_FEWTOKEN_CASE(BN_)                                                                          \
+  if (bn == BN_ && swap) {                                                                             \
+    if (out_dtype == LB_BF16) return launch_fewtoken<BN_, bf16>(map_a, map_b, C, ldc, pb, stream);     \
+    return launch_fewtoken<BN_, float>(map_a, map_b, C, ldc, pb, stream);                              \
+  }
+  LB_FEWTOKEN_CASE(16)
+  LB_FEWTOKEN_CASE(32)
+  LB_FEWTOKEN_CASE(64)
+  LB_FEWTOKEN_CASE(128)
+#undef LB_FEWTOKEN_CASE
+  LB_GEMM_CASE(128, false)
+  LB_GEMM_CASE(256, false)
+#undef LB_GEMM_CASE
+  return LB_ERR_SIZE;
 }

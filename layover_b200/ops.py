@@ -229,7 +229,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None, seed_lo: torc
 # ------------------------------------------------------------------ the bfloat16 path
 BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_mma", "sampling")
 
-_SCRATCH_FLOATS = 4 << 20     # split-K partial tiles (16 MiB)
+_SCRATCH_FLOATS = 8 << 20     # split-K partial tiles (32 MiB)
 _SCRATCH_COUNTERS = 4096
 _scratch: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = {}
 
