@@ -48,7 +48,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -156,15 +156,40 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
   float s[NT_S][4];
 #pragma unroll
   for (int n = 0; n < NT_S; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+  // loads in batches of four before the MMAs that use them, so that neither waits on the other
+  if (PAIRS >= 4) {
 #pragma unroll
-  for (int k = 0; k < KSTEPS; ++k) {
-    if (EXACT || k < dk) {
+    for (int k = 0; k < KSTEPS; ++k) {
+      if (EXACT || k < dk) {
+#pragma unroll
+        for (int n0 = 0; n0 < PAIRS; n0 += 4) {
+          uint32_t b[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) ldmatrix_x4_at(b[u], k_addr + (n0 + u) * 16 * row_bytes + k * 32);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            mma_bf16(s[2 * (n0 + u)], qf[k], b[u][0], b[u][1]);
+            mma_bf16(s[2 * (n0 + u) + 1], qf[k], b[u][2], b[u][3]);
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k0 = 0; k0 < KSTEPS; k0 += 4) {
 #pragma unroll
       for (int n2 = 0; n2 < PAIRS; ++n2) {
-        uint32_t b[4];
-        ldmatrix_x4_at(b, k_addr + n2 * 16 * row_bytes + k * 32);
-        mma_bf16(s[2 * n2], qf[k], b[0], b[1]);
-        mma_bf16(s[2 * n2 + 1], qf[k], b[2], b[3]);
+        uint32_t b[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (EXACT || k0 + u < dk) ldmatrix_x4_at(b[u], k_addr + n2 * 16 * row_bytes + (k0 + u) * 32);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (EXACT || k0 + u < dk) {
+            mma_bf16(s[2 * n2], qf[k0 + u], b[u][0], b[u][1]);
+            mma_bf16(s[2 * n2 + 1], qf[k0 + u], b[u][2], b[u][3]);
+          }
+        }
       }
     }
   }
@@ -225,12 +250,17 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
 #pragma unroll
   for (int kk = 0; kk < PAIRS; ++kk) {
 #pragma unroll
-    for (int n2 = 0; n2 < NT_O / 2; ++n2) {
-      if (EXACT || n2 < dk) {
-        uint32_t b[4];
-        ldmatrix_x4_trans_at(b, v_addr + kk * 16 * row_bytes + n2 * 32);
-        mma_bf16(o[2 * n2], pf[kk], b[0], b[1]);
-        mma_bf16(o[2 * n2 + 1], pf[kk], b[2], b[3]);
+    for (int n0 = 0; n0 < NT_O / 2; n0 += 4) {
+      uint32_t b[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (EXACT || n0 + u < dk) ldmatrix_x4_trans_at(b[u], v_addr + kk * 16 * row_bytes + (n0 + u) * 32);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (EXACT || n0 + u < dk) {
+          mma_bf16(o[2 * (n0 + u)], pf[kk], b[u][0], b[u][1]);
+          mma_bf16(o[2 * (n0 + u) + 1], pf[kk], b[u][2], b[u][3]);
+        }
       }
     }
   }
