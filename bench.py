@@ -218,12 +218,86 @@ def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
             "ms_per_step": 1000.0 * elapsed / steps}
 
 
+def graph_time(fn, calls: int, reps: int = 10) -> float:
+    """Milliseconds per call of `fn(i)`, `calls` of them captured in one CUDA graph and replayed
+    `reps` times: device time of kernels running back to back, without host launch cost."""
+    import torch
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(calls):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(calls):
+            fn(i)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(reps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / reps / calls
+
+
+def kernel_points(args) -> dict:
+    """The dominant kernels alone at the benchmark's shapes, each over rotating operands larger than
+    the L2: the four products of a layer at 8 and 2,048 tokens (with torch.mm, i.e. cuBLAS, beside
+    them for scale) and the decode attention at batch 1, 8 and 64."""
+    import math
+    import torch
+    import layover_b200 as lb
+    from layover_b200 import ops
+
+    cfg = lb.preset(args.model)
+    d, nq, nkv, h, inter = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size, cfg.intermediate_size
+    shapes = {"qkv": ((nq + 2 * nkv) * d, h), "o": (h, nq * d), "gate_up": (2 * inter, h), "down": (h, inter)}
+    ops.gemm_scratch("cuda"); ops.attention_scratch("cuda")
+    out = {"gemm": {}, "attention_decode": {}}
+    for tokens in (8, PREFILL_TOKENS):
+        for name, (n, k) in shapes.items():
+            copies = 24 if tokens <= 128 else 4
+            weights = [(torch.randn(n, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16) for _ in range(copies)]
+            a = torch.randn(tokens, k, device="cuda").to(torch.bfloat16)
+            c = torch.empty(tokens, n, device="cuda", dtype=torch.bfloat16)
+            ours = graph_time(lambda i: ops.gemm_tcgen05(a, weights[i % copies], c), copies)
+            lib = graph_time(lambda i: torch.mm(a, weights[i % copies].T, out=c), copies)
+            out["gemm"][f"{name}_m{tokens}"] = {
+                "us": round(ours * 1e3, 1), "cublas_us": round(lib * 1e3, 1),
+                "tb_s": round(n * k * 2 / ours / 1e9, 2), "tflops": round(2.0 * tokens * n * k / ours / 1e9, 0)}
+            del weights
+    page, ctx = PAGE, (PROMPT + CONTEXT) // 2
+    for batch in (1, 8, 64):
+        pages_per = -(-ctx // page)
+        layers = max(2, min(12, int(2e9 // (batch * pages_per * page * nkv * d * 4))))
+        pools = torch.randn(layers, 2, batch * pages_per + 1, nkv, page, d, device="cuda").to(torch.bfloat16)
+        table = torch.randperm(batch * pages_per, device="cuda").to(torch.int32).view(batch, pages_per)
+        q = torch.randn(batch, nq * d, device="cuda").to(torch.bfloat16)
+        o = torch.empty_like(q)
+        cu = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
+        lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+        splits = ops.decode_splits(batch, nq, nkv, d, ctx, torch.cuda.get_device_properties(0).multi_processor_count)
+        t = graph_time(lambda i: ops.attention_decode_bf16(q, pools[i % layers, 0], pools[i % layers, 1], o, table, cu, lens,
+                                                           None, batch, nq, nkv, d, page, 1 / math.sqrt(d), 0, splits), layers)
+        out["attention_decode"][f"b{batch}_ctx{ctx}"] = {
+            "us": round(t * 1e3, 1), "splits": splits, "tb_s": round(batch * ctx * nkv * d * 4 / t / 1e9, 2)}
+        del pools
+    return {"only": "kernels", **out, "gemm_status": ops.gemm_status()}
+
+
 def run_ours(args) -> dict:
     import torch
     import layover_b200 as lb
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    if args.only == "kernels":
+        return kernel_points(args)
     cfg = lb.preset(args.model)
     layers_full = cfg.num_hidden_layers
     if args.layers:
@@ -377,8 +451,9 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the shape has (both numbers are reported)")
-    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                        help="decode or prefill alone, as a small target for a profiler (prints a short line)")
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
+                        help="decode or prefill alone, as a small target for a profiler, or the dominant kernels "
+                             "alone (prints a short line)")
     args = parser.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
