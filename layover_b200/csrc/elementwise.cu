@@ -337,8 +337,10 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
 // ---------------------------------------------------------------- SwiGLU
 // out[t, j] = silu(gu[t, j]) * gu[t, inter + j], silu(z) = z / (1 + exp(-z)); silu and the
 // product each round to T (layover/model.py:152-153).
+// `block` 0: the row is [all gates | all ups]. `block` b > 0: gates and ups alternate in blocks of b
+// features ([b gates | b ups | b gates | ...]), the layout of the products' fused epilogue.
 template <typename T, bool VEC>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long total, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long total, int inter, int block) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int N = VEC ? Pack<T>::N : 1;
@@ -346,36 +348,40 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   if (idx >= total) return;
   const long t = idx / inter;
   const int j = (int)(idx - t * inter);
-  const T* gp = gate_up + t * 2 * inter + j;
+  const T* gp = gate_up + t * 2 * inter + (block > 0 ? (j / block) * 2 * block + j % block : j);
+  const int up_at = block > 0 ? block : inter;
   if (VEC) {
     float g[Pack<T>::N], u[Pack<T>::N];
     Pack<T>::load(gp, g);
-    Pack<T>::load(gp + inter, u);
+    Pack<T>::load(gp + up_at, u);
 #pragma unroll
     for (int i = 0; i < Pack<T>::N; ++i) g[i] = Elem<T>::round(g[i] / (1.0f + expf(-g[i]))) * u[i];
     Pack<T>::store(out + idx, g);
   } else {
-    const float g = Elem<T>::load(gp), u = Elem<T>::load(gp + inter);
+    const float g = Elem<T>::load(gp), u = Elem<T>::load(gp + up_at);
     Elem<T>::store(out + idx, Elem<T>::round(g / (1.0f + expf(-g))) * u);
   }
 }
 
 template <typename T>
-static int launch_swiglu(const void* gate_up, void* out, long total, int inter, cudaStream_t stream) {
+static int launch_swiglu(const void* gate_up, void* out, long total, int inter, int block, cudaStream_t stream) {
   constexpr int N = Pack<T>::N;
-  const bool vec = inter % N == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0;
+  const bool vec = inter % N == 0 && (block == 0 || block % N == 0) && (uintptr_t)gate_up % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0;
   const int threads = 256;
   const long work = vec ? total / N : total;
   const unsigned blocks = (unsigned)((work + threads - 1) / threads);
-  if (vec) lb_launch(swiglu_kernel<T, true>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter);
-  else lb_launch(swiglu_kernel<T, false>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter);
+  if (vec) lb_launch(swiglu_kernel<T, true>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter, block);
+  else lb_launch(swiglu_kernel<T, false>, blocks, threads, 0, stream, (const T*)gate_up, (T*)out, total, inter, block);
   return lb_last_error();
 }
 
-LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, int inter, cudaStream_t stream) {
+LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, int inter, int block,
+                        cudaStream_t stream) {
   const long total = (long)tokens * inter;
   if (total <= 0) return 0;
-  if (dtype == LB_F32) return launch_swiglu<float>(gate_up, out, total, inter, stream);
-  if (dtype == LB_BF16) return launch_swiglu<bf16>(gate_up, out, total, inter, stream);
+  if (block < 0 || (block > 0 && inter % block)) return LB_ERR_SIZE;
+  if (dtype == LB_F32) return launch_swiglu<float>(gate_up, out, total, inter, block, stream);
+  if (dtype == LB_BF16) return launch_swiglu<bf16>(gate_up, out, total, inter, block, stream);
   return LB_ERR_DTYPE;
 }

@@ -144,6 +144,19 @@ template <> __device__ __forceinline__ void store_row16<bf16>(bf16* p, const flo
 // two accumulators, so the epilogue of one tile overlaps the MMAs of the next.
 constexpr int SMALL_THREADS = 128;
 
+// silu(g) * u as the reference's bfloat16 tensors compute it: the two projections round to bf16,
+// the activation rounds to bf16, the product rounds when it is stored (layover/model.py:152-153).
+__device__ __forceinline__ float swiglu_bf16(float g, float u) {
+  g = __bfloat162float(__float2bfloat16_rn(g));
+  u = __bfloat162float(__float2bfloat16_rn(u));
+  const float act = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
+  return act * u;
+}
+
+// With the SwiGLU epilogue the weight's rows come in blocks of 128: 64 gate rows of features
+// f .. f + 63, then the 64 up rows of the same features. A product tile then holds both halves of
+// every feature it covers, and the kernel writes silu(gate) * up, half as many columns as the
+// product has: C[token, feature].
 // The few-token orientation keeps two blocks on an SM (half the shared memory each), so that a
 // weight matrix with about as many tiles as SMs, or one split in two, still runs in one wave.
 template <int BN> struct SmallTile {
@@ -161,7 +174,7 @@ template <int BN> struct SmallTile {
 // One tile (or one K range of a tile) per block, two blocks per SM, four warps that all join the
 // epilogue: for these short streams it starts and ends a few microseconds sooner than the
 // persistent kernel below.
-template <int BN, typename OutT>
+template <int BN, typename OutT, int EPI>
 __global__ void __launch_bounds__(SMALL_THREADS, SmallTile<BN>::BLOCKS_PER_SM)
 gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, int K, int splits,
@@ -256,6 +269,22 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           if (c + i < valid_cols) my_partial[(size_t)(c + i) * BM + row] = v[i];
+      } else if (EPI == 1) {
+        // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same features: the
+        // upper half hands its values over through shared memory (the ring is drained by now)
+        float* handover = reinterpret_cast<float*>(tiles_a);           // [64][17]
+        if (row >= 64) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) handover[(row - 64) * 17 + i] = v[i];
+        }
+        __syncthreads();
+        if (row < 64 && m0 + row < rows_a) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c + i < valid_cols)
+              store_one<OutT>(C + (size_t)(n0 + c + i) * ldc + (m0 >> 1) + row, swiglu_bf16(v[i], handover[row * 17 + i]));
+        }
+        __syncthreads();
       } else if (true) {
         if (m0 + row < rows_a) {
 #pragma unroll
@@ -389,7 +418,7 @@ constexpr int PERSISTENT_THREADS = (2 + EPILOGUE_WARPS) * 32;
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // D[i, j] = sum_k Aop[i, k] Bop[j, k], i on the 128-row side. SWAP false: C[i, j] = D; true: C[j, i] = D.
-template <int BN, bool SWAP, typename OutT>
+template <int BN, bool SWAP, typename OutT, int EPI>
 __global__ void __launch_bounds__(PERSISTENT_THREADS, Tile<BN, SWAP>::BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, const Schedule sch,
@@ -515,7 +544,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int valid_cols = min(BN, rows_b - n0);
       const int slot = seg.tile - sch.full * blocks;         // index among the last round's tiles
       float* my_partial = seg.splits > 1 ? partials + ((size_t)slot * seg.splits + seg.split) * BN * BM : nullptr;
-      for (int c = 0; c < BN; c += 16) {
+      if (EPI == 1 && seg.splits == 1) {
+        // columns come as [64 gate | 64 up] per 128: one thread holds both halves of its token's
+        // features and writes 64 activations per 128 columns
+        for (int half = 0; half * 128 < valid_cols; ++half) {
+#pragma unroll
+          for (int cc = 0; cc < 64; cc += 16) {
+            float g[16], u[16];
+            tmem_ld16(lane_base + half * 128 + cc, g);
+            tmem_ld16(lane_base + half * 128 + 64 + cc, u);
+            if (m0 + row < rows_a) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) g[i] = swiglu_bf16(g[i], u[i]);
+              OutT* dst = C + (size_t)(m0 + row) * ldc + (n0 >> 1) + half * 64 + cc;
+              if (vector_ok) {
+                store_row16<OutT>(dst, g);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) store_one<OutT>(dst + i, g[i]);
+              }
+            }
+          }
+        }
+      }
+      for (int c = 0; c < BN && !(EPI == 1 && seg.splits == 1); c += 16) {
         if (c >= valid_cols) break;                           // uniform over the block
         float v[16];
         tmem_ld16(lane_base + c, v);
@@ -575,7 +627,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const int quads = (valid_cols + 3) >> 2;                      // groups of four columns
           const int share = (quads + seg.splits - 1) / seg.splits;
           const int q_begin = seg.split * share, q_end = min(quads, q_begin + share);
-          if (m0 + row < rows_a) {
+          if (EPI == 1) {
+            // shares of OUTPUT quads: output quad o of a 128-column half h sums gate quad
+            // 32 h + o and up quad 32 h + 16 + o over the splits, then combines them
+            const int out_quads = valid_cols >> 3;
+            const int out_share = (out_quads + seg.splits - 1) / seg.splits;
+            const int o_begin = seg.split * out_share, o_end = min(out_quads, o_begin + out_share);
+            if (m0 + row < rows_a) {
+              for (int oq = o_begin; oq < o_end; ++oq) {
+                const int gq = (oq >> 4) * 32 + (oq & 15), uq = gq + 16;
+                float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+#pragma unroll 4
+                for (int s0 = 0; s0 < seg.splits; ++s0) {
+                  const float4 pg = tile_partials[((size_t)s0 * (BN / 4) + gq) * BM + row];
+                  const float4 pu = tile_partials[((size_t)s0 * (BN / 4) + uq) * BM + row];
+                  g.x += pg.x; g.y += pg.y; g.z += pg.z; g.w += pg.w;
+                  u.x += pu.x; u.y += pu.y; u.z += pu.z; u.w += pu.w;
+                }
+                OutT* dst = C + (size_t)(m0 + row) * ldc + (n0 >> 1) + oq * 4;
+                store_one<OutT>(dst, swiglu_bf16(g.x, u.x));
+                store_one<OutT>(dst + 1, swiglu_bf16(g.y, u.y));
+                store_one<OutT>(dst + 2, swiglu_bf16(g.z, u.z));
+                store_one<OutT>(dst + 3, swiglu_bf16(g.w, u.w));
+              }
+            }
+          } else if (m0 + row < rows_a) {
             for (int q0 = q_begin; q0 < q_end; q0 += 4) {
               float4 sum[4];
 #pragma unroll
@@ -690,11 +766,11 @@ struct Problem {
   int n_counters;
 };
 
-template <int BN, bool SWAP, typename OutT>
+template <int BN, bool SWAP, typename OutT, int EPI = 0>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb, bool vector_ok,
            cudaStream_t stream) {
   using T = Tile<BN, SWAP>;
-  auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT>;
+  auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
   static int blocks_per_sm = 0;      // how many blocks of this kernel an SM really holds
   if (blocks_per_sm == 0) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
@@ -747,11 +823,11 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
   return code ? code : lb_last_error();
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, int EPI = 0>
 int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb,
                     cudaStream_t stream) {
   using T = SmallTile<BN>;
-  auto kernel = gemm_fewtoken_kernel<BN, OutT>;
+  auto kernel = gemm_fewtoken_kernel<BN, OutT, EPI>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
@@ -760,7 +836,7 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
   }
   const int tiles = (pb.rows_a + BM - 1) / BM, total_kb = (pb.K + BK - 1) / BK;
   int splits = 1;
-  if (pb.scratch && pb.counters && tiles <= pb.n_counters && tiles < pb.sm_count) {
+  if (EPI == 0 && pb.scratch && pb.counters && tiles <= pb.n_counters && tiles < pb.sm_count) {
     // One block per SM streams a weight matrix at close to full bandwidth, and every further
     // split adds a partial tile to write, a fence, a counter and a longer sum, which at these
     // sizes cost more than the extra blocks win (measured on 2560..9728-wide weights: 8 splits
@@ -799,11 +875,14 @@ LB_EXPORT int lb_gemm_tcgen05_supports(const void* A, const void* W, int K, long
 
 // C[M, N] = A[M, K] W[N, K]^T. out_dtype: LB_BF16 or LB_F32. `scratch` (floats) and `counters`
 // (zeroed once by the caller, `n_counters` of them) serve the split-K path; without them K is
-// never split. `sm_count` sizes the grid; `max_splits` > 0 caps the splitting.
+// never split. `sm_count` sizes the grid; `max_splits` > 0 caps the splitting. `epilogue` 1: W's rows
+// come as blocks of 64 gate rows + 64 up rows and C[M, N / 2] = silu(gate) * up (bfloat16 only).
 LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K, long lda,
                               long ldw, long ldc, float* scratch, long scratch_floats, unsigned* counters,
-                              int n_counters, int sm_count, int max_splits, cudaStream_t stream) {
+                              int n_counters, int sm_count, int max_splits, int epilogue, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (epilogue != 0 && epilogue != 1) return LB_ERR_SIZE;
+  if (epilogue == 1 && (N % 128 != 0 || out_dtype != LB_BF16)) return LB_ERR_SIZE;   // blocks of 64 gate + 64 up rows
   if (!lb_gemm_tcgen05_supports(A, W, K, lda, ldw)) return LB_ERR_ALIGN;
   if (out_dtype != LB_BF16 && out_dtype != LB_F32) return LB_ERR_DTYPE;
   if (sm_count < 1) sm_count = 1;
@@ -833,6 +912,16 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
   if (bn == BN_ && swap) {                                                                             \
     if (out_dtype == LB_BF16) return launch_fewtoken<BN_, bf16>(map_a, map_b, C, ldc, pb, stream);     \
     return launch_fewtoken<BN_, float>(map_a, map_b, C, ldc, pb, stream);                              \
+  }
+  if (epilogue == 1) {
+    if (swap) {
+      if (bn == 16) return launch_fewtoken<16, bf16, 1>(map_a, map_b, C, ldc, pb, stream);
+      if (bn == 32) return launch_fewtoken<32, bf16, 1>(map_a, map_b, C, ldc, pb, stream);
+      if (bn == 64) return launch_fewtoken<64, bf16, 1>(map_a, map_b, C, ldc, pb, stream);
+      return launch_fewtoken<128, bf16, 1>(map_a, map_b, C, ldc, pb, stream);
+    }
+    if (bn == 128) return launch<128, false, bf16, 1>(map_a, map_b, C, ldc, pb, vector_ok, stream);
+    return launch<256, false, bf16, 1>(map_a, map_b, C, ldc, pb, vector_ok, stream);
   }
   // 32..128 tokens and a weight with fewer 128-row tiles than SMs: the persistent kernel, whose
   // blocks add up the partial tiles together, takes 8 splits well (measured: 11 us against 18 us

@@ -23,6 +23,20 @@ def _linear_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None
     return ops.gemm_bf16(a, w, out)
 
 
+def _linear_swiglu_bf16(a: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor | None:
+    """silu(a Wg^T) * (a Wu^T) over interleaved weights. Many tokens: one product with the activation
+    in its epilogue (the [T, 2 I] tensor is never written). Few tokens: product, then the activation
+    kernel, which hides behind its neighbours there (measured: 31.3 us against 31.7 us fused for a
+    whole feed-forward at one token, 41.4 against 43.5 at 64)."""
+    tokens, inter = a.shape[0], w_interleaved.shape[0] // 2
+    out = torch.empty((tokens, inter), dtype=torch.bfloat16, device=a.device)
+    if tokens > 128 and ops.gemm_tcgen05_supports(a, w_interleaved):
+        return ops.gemm_tcgen05(a, w_interleaved, out, epilogue="swiglu")
+    gate_up = torch.empty((tokens, 2 * inter), dtype=torch.bfloat16, device=a.device)
+    ops.gemm_bf16(a, w_interleaved, gate_up)
+    return ops.swiglu(gate_up, out, block=ops.SWIGLU_BLOCK)
+
+
 def _attention_simt(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
     tiles = batch.tiles[ops.attention_simt_block_queries()]
     ops.attention_simt(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
@@ -43,6 +57,9 @@ def make_runtime(dtype: torch.dtype, device: torch.device | str) -> Runtime:
         ops.attention_scratch(device)
         runtime = Runtime(dtype, device, _linear_bf16)
         runtime.attention = ops.attention_bf16
+        runtime.linear_swiglu = _linear_swiglu_bf16
+        runtime.swiglu_block = ops.SWIGLU_BLOCK
+        runtime.interleave_gate_up = ops.interleave_gate_up
         runtime.tile_sizes = ops.attention_bf16_tile_sizes()
         runtime.kernel_libraries = ops.BF16_LIBRARIES
     else:

@@ -147,14 +147,16 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor | None, k_pool: torch
               page_tokens, float(eps), _stream()), "qk_norm_rope_kv")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:], gate_up [T, 2 I], out [T, I]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Tensor:
+    """out = silu(gate) * up, gate_up [T, 2 I], out [T, I]. block 0: the row is [all gates | all ups];
+    block b: gates and ups alternate in blocks of b features (`interleave_gate_up`'s layout)."""
     _need(gate_up, None, "gate_up"); _need(out, gate_up.dtype, "out")
     inter = gate_up.shape[1] // 2
     if gate_up.shape[1] != 2 * inter or out.shape[1] != inter or out.shape[0] != gate_up.shape[0]:
         raise ValueError("swiglu: shapes do not agree")
-    fn = _fn("elementwise", "lb_swiglu", [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(dtype_code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inter, _stream()), "swiglu")
+    fn = _fn("elementwise", "lb_swiglu", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inter, int(block), _stream()),
+           "swiglu")
     return out
 
 
@@ -253,21 +255,44 @@ def gemm_tcgen05_supports(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1)
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, max_splits: int = 0) -> torch.Tensor:
-    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores; bfloat16 in, out bfloat16 or float32."""
+SWIGLU_BLOCK = 64   # gate and up rows alternate in blocks of this many features for the fused epilogue
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2 I, H] with rows in blocks of 64 gate rows followed by the 64 up rows of the same features:
+    the layout `gemm_tcgen05(..., epilogue="swiglu")` wants. I must be a multiple of 64."""
+    inter, hidden = gate.shape
+    if inter % SWIGLU_BLOCK or up.shape != gate.shape:
+        raise ValueError("interleave_gate_up: the width must be a multiple of 64 and the shapes must agree")
+    blocks = inter // SWIGLU_BLOCK
+    stacked = torch.stack((gate.view(blocks, SWIGLU_BLOCK, hidden), up.view(blocks, SWIGLU_BLOCK, hidden)), dim=1)
+    return stacked.reshape(2 * inter, hidden).contiguous()
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, max_splits: int = 0,
+                 epilogue: str | None = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores; bfloat16 in, out bfloat16 or float32.
+
+    epilogue "swiglu": w's rows are interleaved by `interleave_gate_up` and out[M, N / 2] = silu(gate) * up,
+    rounded where the reference's bfloat16 tensors round."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
         raise ValueError("gemm_tcgen05: operands must be 2-D bfloat16")
     m, k = a.shape
     n = w.shape[0]
-    if w.shape[1] != k or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+    if epilogue not in (None, "swiglu"):
+        raise ValueError(f"gemm_tcgen05: unknown epilogue {epilogue!r}")
+    out_cols = n // 2 if epilogue == "swiglu" else n
+    if epilogue == "swiglu" and (n % (2 * SWIGLU_BLOCK) or out.dtype != torch.bfloat16):
+        raise ValueError("gemm_tcgen05: the swiglu epilogue needs interleaved weights (2 I rows, I % 64 == 0) and a bfloat16 output")
+    if w.shape[1] != k or tuple(out.shape) != (m, out_cols) or out.stride(1) != 1:
         raise ValueError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     partials, counters, sms = gemm_scratch(a.device)
     fn = _fn("gemm_tcgen05", "lb_gemm_tcgen05",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long, c_long, c_void_p, c_long,
-              c_void_p, c_int, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
-              _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), sms, int(max_splits), _stream()),
-           "gemm_tcgen05")
+              _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), sms, int(max_splits),
+              1 if epilogue == "swiglu" else 0, _stream()), "gemm_tcgen05")
     return out
 
 

@@ -64,6 +64,10 @@ class Runtime:
     linear: Callable[..., torch.Tensor]   # linear(a [M, K], w [N, K], out_dtype=None) -> [M, N]
     # attention(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window)
     attention: Callable[..., None] | None = None
+    # linear_swiglu(a, w_interleaved) -> silu(gate) * up or None; w made by interleave_gate_up(gate, up)
+    linear_swiglu: Callable[..., torch.Tensor | None] | None = None
+    interleave_gate_up: Callable[..., torch.Tensor] | None = None
+    swiglu_block: int = 0                 # the fused product wants the width to be a multiple of this
     tile_sizes: tuple[int, ...] = ()      # query-tile sizes whose tile lists the batch must carry
     kernel_libraries: tuple[str, ...] = ()  # what has to be compiled before the first step
 

@@ -100,6 +100,11 @@ def test_swiglu(dtype, tokens, inter):
     ops().swiglu(gu, out)
     expected = torch.nn.functional.silu(gu[:, :inter].cpu()) * gu[:, inter:].cpu()
     close(out, expected, dtype)
+    if inter % 8 == 0:       # gates and ups alternating in blocks of 8 features
+        mixed = torch.stack((gu[:, :inter].view(tokens, -1, 8), gu[:, inter:].view(tokens, -1, 8)), dim=2).reshape(tokens, -1)
+        out2 = torch.empty_like(out)
+        ops().swiglu(mixed.contiguous(), out2, block=8)
+        assert torch.equal(out2, out)
 
 
 def paged_setup(dtype, lengths, kv_heads, dim, page, seed=0, poison=True):
@@ -403,3 +408,25 @@ def test_bf16_attention_finds_one_far_key_among_thousands(kernel, far_key):
     else:
         o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, n * one, None, 1, 1, 1, dim, 16, 1.0 / math.sqrt(dim), 0, 7)
     assert (out.float().cpu() - 7.0).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("m, inter, k", [(1, 64, 64), (8, 9728, 2560), (17, 128, 96), (64, 192, 200), (128, 1024, 256),
+                                         (129, 64, 64), (300, 448, 136), (2048, 1280, 512), (2048, 9728, 256)])
+def test_gemm_tcgen05_swiglu_epilogue(m, inter, k):
+    o = ops()
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn(inter, k, device="cuda") * 2 / math.sqrt(k)).to(torch.bfloat16)
+    up = (torch.randn(inter, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
+    w = o.interleave_gate_up(gate, up)
+    assert w.shape == (2 * inter, k) and torch.equal(w[:64], gate[:64]) and torch.equal(w[64:128], up[:64])
+    g = (a.double() @ gate.double().T).float().to(torch.bfloat16)
+    u = (a.double() @ up.double().T).float().to(torch.bfloat16)
+    expected = (torch.nn.functional.silu(g) * u).float()
+    for _ in range(2):
+        out = torch.full((m, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+        o.gemm_tcgen05(a, w, out, epilogue="swiglu")
+        assert o.gemm_status() == 0
+        assert not torch.isnan(out).any()
+        close(out, expected, torch.bfloat16)
+    with pytest.raises(ValueError, match="swiglu"):
+        o.gemm_tcgen05(a, w[:2 * inter - 64], torch.empty(m, inter - 32, device="cuda", dtype=torch.bfloat16), epilogue="swiglu")
