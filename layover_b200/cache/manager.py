@@ -57,6 +57,7 @@ class CacheView:
     writes: bool = True                # False when the entry reads another entry's keys and values
     k_pool: torch.Tensor | None = None # [pages + 1, kv_heads, page_tokens, head_dim]
     v_pool: torch.Tensor | None = None
+    pool: torch.Tensor | None = None   # the group's whole pool [layers, 2, pages + 1, kv_heads, page_tokens, head_dim]
     state: torch.Tensor | None = None  # [slots + 1, *shape]
     page_tokens: int = 0
     need: object = None
@@ -138,7 +139,7 @@ class CacheManager:
         for view in self.views.values():
             if view.kind == "paged":
                 pool = self.paged[view.group].pool
-                view.k_pool, view.v_pool = pool[view.layer, 0], pool[view.layer, 1]
+                view.k_pool, view.v_pool, view.pool = pool[view.layer, 0], pool[view.layer, 1], pool
             else:
                 view.state = self.states[view.group].pool[view.layer]
 

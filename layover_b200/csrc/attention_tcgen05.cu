@@ -1,0 +1,622 @@
+// Paged grouped-query attention for bfloat16 on the 5th-generation tensor cores: both products of
+// attention (S = Q K^T and O = P V) are tcgen05.mma with accumulators in tensor memory, K and V
+// pages come by TMA straight from the block table, and the softmax runs one thread per query row.
+// The reference gathers the history out of its pool and calls a library kernel for prompts
+// (layover/model.py:84-90) and a Triton program per (sequence, head) for decode
+// (layover/kernels/triton_decode.py:39-119).
+//
+// One kernel, two row mappings of the 128-row query tile:
+//   prompt portions  rows = 128 consecutive tokens of one query head of one sequence
+//   decode           rows = the query heads that share one KV head, for a sequence's single new
+//                    token (rows past the group are ballast); the context is split over several
+//                    blocks, whose partial (reference maximum, sum, output) are merged by the block
+//                    that arrives last at the (sequence, KV head) counter
+//
+// Block = 6 warps: warp 0 lane 0 walks the block table and issues one 5-D TMA copy per page and
+// half of the head (the whole cache group's pool is ONE tensor map: dim, slot, KV head, page,
+// layer x {K, V}); warp 1 lane 0 issues the MMAs; warps 2-5 own one query row per thread: they
+// read the row's 128 scores from tensor memory, keep the running maximum and sum, write the
+// probabilities as the bf16 A operand of the second product and rescale the output only when the
+// maximum has grown by more than 2^8 (the accumulated values stay exact relative to a reference
+// maximum; the final division uses the same reference). Every mbarrier wait is bounded.
+//
+// Limits: head size 128, page size a multiple of 8 that divides 128, at most 128 query heads per KV
+// head in decode; anything else is refused (the mma.sync kernels of attention_mma.cu take it).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS = 128;        // query rows per block (the MMA's M)
+constexpr int KEYS = 128;        // keys per tile (N of the first product, K of the second)
+constexpr int DIM = 128;         // head size
+constexpr int HALF_BYTES = ROWS * 128;          // one 64-column half of a 128-row operand: 16 KiB
+constexpr int TILE_BYTES = 2 * HALF_BYTES;      // 32 KiB
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr float RESCALE_THRESHOLD = 8.0f;       // in log2 units
+
+__device__ int g_attn_error = 0;   // 0 = ok; which wait ran out otherwise
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+    if (spin > 1024) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory matrix descriptors, 128-byte swizzle, version 1.
+// K-major (rows of 128 bytes, 8-row groups 1024 bytes apart): Q, K and P.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+// MN-major (the same bytes read with the 128-byte rows running along N): V as the B operand of
+// O = P V. Leading offset: from one 64-column block of the head to the next (the other half of the
+// tile); stride offset: from one group of 8 keys to the next.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  const uint32_t lo = ((addr >> 4) & 0x3FFFu) | ((uint32_t)(HALF_BYTES >> 4) << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+// bf16 x bf16 -> f32, M = 128, N = 128; b_mn: B is MN-major
+constexpr uint32_t instr_desc(bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+struct Args {
+  bf16* out;
+  const int* block_table;
+  int table_width;
+  const int* cu_q;
+  const int* ctx_len;
+  const int* tile_seq;      // prompt portions: the tile list; decode: null
+  const int* tile_q0;
+  int q_heads, kv_heads, page_tokens, window;
+  int layer2;               // 2 * layer: the K plane of this layer in the pool's last dimension
+  float scale_log2;
+  int splits;               // decode only
+  float* partials;
+  unsigned* counters;
+};
+
+constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * KV_STAGES) + 1024 + 512;   // Q, P, K and V stages, slack, barriers
+
+template <bool DECODE>
+__global__ void __launch_bounds__(THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                         const Args args) {
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* p_s = q_s + TILE_BYTES;
+  uint8_t* k_s = p_s + TILE_BYTES;                       // [KV_STAGES][TILE_BYTES]
+  uint8_t* v_s = k_s + KV_STAGES * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2]
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [2] scores of a tile are in tensor memory
+  uint64_t* s_empty = bars + 11;      // [2] the softmax has read them
+  uint64_t* p_full = bars + 13;       // the probabilities are in shared memory, the output is rescaled
+  uint64_t* pv_done = bars + 14;      // the second product of a tile is finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile uint32_t* flag = tmem_slot + 1;   // [0] a wait ran out, [1] last block of its (sequence, KV head)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- what this block works on
+  int seq, head, kv_head, q_row, n_rows, p_first, p_last, tile_begin, tile_end, key_lo;
+  const int group = args.q_heads / args.kv_heads;
+  if (DECODE) {
+    seq = blockIdx.x; kv_head = blockIdx.y; head = kv_head * group;
+    const int ctx = args.ctx_len[seq];
+    p_first = p_last = ctx - 1;
+    key_lo = args.window > 0 ? max(0, p_last - args.window + 1) : 0;
+    const int first_tile = key_lo / KEYS, n_tiles = p_last / KEYS + 1 - first_tile;
+    const int per_split = (n_tiles + args.splits - 1) / args.splits;
+    tile_begin = first_tile + blockIdx.z * per_split;
+    tile_end = min(first_tile + n_tiles, tile_begin + per_split);
+    q_row = args.cu_q[seq] * args.q_heads + head;     // row of q viewed as [tokens * heads, dim]
+    n_rows = group;
+  } else {
+    seq = args.tile_seq[blockIdx.x];
+    const int q0 = args.tile_q0[blockIdx.x];
+    head = blockIdx.y; kv_head = head / group;
+    const int row0 = args.cu_q[seq], q_len = args.cu_q[seq + 1] - row0, ctx = args.ctx_len[seq];
+    n_rows = min(ROWS, q_len - q0);
+    p_first = ctx - q_len + q0; p_last = p_first + n_rows - 1;
+    key_lo = args.window > 0 ? max(0, p_first - args.window + 1) : 0;
+    tile_begin = key_lo / KEYS; tile_end = p_last / KEYS + 1;
+    q_row = row0 + q0;                                   // row of q viewed as [tokens, heads * dim]
+  }
+  const int n_tiles_mine = max(0, tile_end - tile_begin);
+  const int* table = args.block_table + (size_t)seq * args.table_width;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    flag[0] = 0; flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;            // two score buffers of 128 columns
+  const uint32_t tmem_o = tmem_base + 256;      // the output accumulator, 128 columns
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles_mine > 0) {
+      // ---------------- producer: the query tile, then K and V page by page
+      mbar_expect_tx(q_full, TILE_BYTES);
+      for (int half = 0; half < 2; ++half)
+        tma_load_2d(q_s + half * HALF_BYTES, &q_map, q_full, (DECODE ? 0 : head * DIM) + half * 64, q_row);
+      const int pages_per_tile = KEYS / args.page_tokens;
+      for (int i = 0; i < n_tiles_mine && !flag[0]; ++i) {
+        const int tile = tile_begin + i, stage = i % KV_STAGES;
+        const uint32_t phase = (i / KV_STAGES) & 1;
+        for (int kind = 0; kind < 2; ++kind) {       // K first: the first product needs it first
+          uint64_t* empty = kind ? &v_empty[stage] : &k_empty[stage];
+          uint64_t* full = kind ? &v_full[stage] : &k_full[stage];
+          uint8_t* dst = (kind ? v_s : k_s) + stage * TILE_BYTES;
+          if (!mbar_wait(empty, phase ^ 1)) { atomicCAS(&g_attn_error, 0, 1); flag[0] = 1; break; }
+          mbar_expect_tx(full, TILE_BYTES);
+          for (int pg = 0; pg < pages_per_tile; ++pg) {
+            const int index = min(tile * pages_per_tile + pg, args.table_width - 1);   // past the table: any page, masked anyway
+            const int page = table[index];
+            for (int half = 0; half < 2; ++half)
+              tma_load_5d(dst + half * HALF_BYTES + pg * args.page_tokens * 128, &kv_map, full, half * 64, 0, kv_head, page,
+                          args.layer2 + kind);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles_mine > 0) {
+      // ---------------- MMA issuer: S(i + 1) = Q K^T is issued before O += P(i) V, so that the
+      // softmax of one tile overlaps the first product of the next
+      constexpr uint32_t idesc_s = instr_desc(false), idesc_o = instr_desc(true);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) { atomicCAS(&g_attn_error, 0, 2); flag[0] = 1; }
+      auto issue_s = [&](int i) {
+        const int stage = i % KV_STAGES, buf = i & 1;
+        if (!mbar_wait(&k_full[stage], (i / KV_STAGES) & 1) || !mbar_wait(&s_empty[buf], ((i >> 1) & 1) ^ 1)) {
+          atomicCAS(&g_attn_error, 0, 3); flag[0] = 1; return false;
+        }
+        fence_after_sync();
+        const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s + stage * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < DIM / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_bf16(tmem_s + buf * 128, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[buf]);
+        umma_commit(&k_empty[stage]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int i = 0; i < n_tiles_mine && ok; ++i) {
+        if (i + 1 < n_tiles_mine) ok = issue_s(i + 1);
+        if (!ok) break;
+        const int stage = i % KV_STAGES;
+        if (!mbar_wait(p_full, i & 1) || !mbar_wait(&v_full[stage], (i / KV_STAGES) & 1)) {
+          atomicCAS(&g_attn_error, 0, 4); flag[0] = 1; break;
+        }
+        fence_after_sync();
+        const uint32_t p_addr = smem_u32(p_s), v_addr = smem_u32(v_s + stage * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < KEYS / 16; ++ks) {
+          const uint32_t a_off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;     // 16 keys along P's rows
+          const uint32_t b_off = ks * 16 * 128;                               // 16 key rows of V
+          umma_bf16(tmem_o, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(pv_done);
+        umma_commit(&v_empty[stage]);
+      }
+    }
+  } else {
+    // ---------------- softmax and epilogue: one query row per thread
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int p_row = DECODE ? p_last : p_first + row;        // rows past n_rows are ballast
+    const float c = args.scale_log2;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles_mine && ok; ++i) {
+      const int tile = tile_begin + i, buf = i & 1, stage = i % KV_STAGES;
+      const int key0 = tile * KEYS;
+      if (!mbar_wait(&s_full[buf], (i >> 1) & 1)) { atomicCAS(&g_attn_error, 0, 5); flag[0] = 1; ok = false; break; }
+      fence_after_sync();
+      // the tile needs the comparisons if it reaches past the block's first position, starts before
+      // the first visible key, or a window cuts it
+      const bool masked = key0 + KEYS - 1 > p_first || key0 < key_lo || args.window > 0;
+      float s[KEYS];
+#pragma unroll
+      for (int ch = 0; ch < KEYS / 16; ++ch) {
+        float v[16];
+        tmem_ld16(tmem_s + buf * 128 + lane_addr + ch * 16, v);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) s[ch * 16 + e] = v[e];
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);
+      float tile_max = -INFINITY;
+      if (masked) {
+#pragma unroll
+        for (int e = 0; e < KEYS; ++e) {
+          const int key = key0 + e;
+          const bool seen = key <= p_row && key >= key_lo && (args.window <= 0 || p_row - key < args.window);
+          if (!seen) s[e] = -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < KEYS; ++e) tile_max = fmaxf(tile_max, s[e]);
+      // The reference maximum only moves when the true one has outgrown it by 2^8: the accumulated
+      // output then needs no rescaling for most tiles. A warp rescales together (tensor-memory
+      // loads and stores are warp-wide), every lane by its own factor.
+      const bool grow = (tile_max - m_ref) * c > RESCALE_THRESHOLD || (m_ref == -INFINITY && tile_max > -INFINITY);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
+      // the previous tile's second product must be done before P is overwritten or O is touched
+      if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) { atomicCAS(&g_attn_error, 0, 6); flag[0] = 1; ok = false; break; }
+      fence_after_sync();
+      if (any_grow) {
+        const float m_new = grow ? tile_max : m_ref;
+        const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * c);
+        if (i > 0) {
+#pragma unroll
+          for (int ch = 0; ch < DIM / 16; ++ch) {
+            float v[16];
+            tmem_ld16(tmem_o + lane_addr + ch * 16, v);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] *= factor;
+            tmem_st16(tmem_o + lane_addr + ch * 16, v);
+          }
+        }
+        l_sum *= factor;
+        m_ref = m_new;
+      }
+      const float neg_base = (m_ref == -INFINITY) ? 0.f : -m_ref * c;
+      // probabilities as bf16 into the A operand of the second product: row `row`, 16-byte pieces
+      // of 8 keys, swizzled like every 128-byte row
+#pragma unroll
+      for (int piece = 0; piece < KEYS / 8; ++piece) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = fast_exp2(fmaf(s[piece * 8 + 2 * e], c, neg_base));
+          const float b = fast_exp2(fmaf(s[piece * 8 + 2 * e + 1], c, neg_base));
+          l_sum += a + b;
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+          w[e] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        const int half = piece >> 3, chunk = piece & 7;
+        uint8_t* dst = p_s + half * HALF_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      // V rows of keys that are not part of the context may hold anything (a stale or poisoned
+      // page): zero them, since 0 x NaN would still be NaN. Only boundary tiles have such rows.
+      const int limit = p_last + 1;
+      if (key0 + KEYS > limit || key0 < key_lo) {
+        if (!mbar_wait(&v_full[stage], (i / KV_STAGES) & 1)) { atomicCAS(&g_attn_error, 0, 7); flag[0] = 1; ok = false; break; }
+        const int key = key0 + row;
+        if (key >= limit || key < key_lo) {
+          uint8_t* vrow = v_s + stage * TILE_BYTES + row * 128;
+#pragma unroll
+          for (int chunk = 0; chunk < 8; ++chunk) {
+            *reinterpret_cast<uint4*>(vrow + chunk * 16) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vrow + HALF_BYTES + chunk * 16) = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+      fence_async_smem();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+
+    // ---- the block's result: wait for the last second product, read the row, divide, store
+    float* my_partial = nullptr;
+    const int mstride = DIM + 2;
+    const unsigned tile_id = DECODE ? blockIdx.x * gridDim.y + blockIdx.y : 0;
+    if (DECODE && args.splits > 1)
+      my_partial = args.partials + ((size_t)tile_id * args.splits + blockIdx.z) * group * mstride;
+    if (ok && n_tiles_mine > 0) {
+      if (!mbar_wait(pv_done, (n_tiles_mine - 1) & 1)) { atomicCAS(&g_attn_error, 0, 8); flag[0] = 1; ok = false; }
+      fence_after_sync();
+    }
+    if (ok) {
+      const bool valid = row < n_rows;
+      bf16* dst = nullptr;
+      if (valid) {
+        if (DECODE) dst = args.out + ((size_t)args.cu_q[seq] * args.q_heads + head + row) * DIM;
+        else dst = args.out + ((size_t)(q_row + row) * args.q_heads + head) * DIM;
+      }
+      const float inv = 1.0f / l_sum;
+#pragma unroll
+      for (int ch = 0; ch < DIM / 16; ++ch) {
+        float v[16];
+        if (n_tiles_mine > 0) {
+          tmem_ld16(tmem_o + lane_addr + ch * 16, v);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = 0.f;
+        }
+        if (!valid) continue;
+        if (my_partial) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) my_partial[row * mstride + ch * 16 + e] = v[e];
+        } else {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * e] * inv, v[2 * e + 1] * inv);
+            w[e] = *reinterpret_cast<const uint32_t*>(&pair);
+          }
+          reinterpret_cast<uint4*>(dst + ch * 16)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          reinterpret_cast<uint4*>(dst + ch * 16)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+      if (my_partial && valid) {     // the reference maximum in the units of the exponent, and the sum
+        my_partial[row * mstride + DIM] = (m_ref == -INFINITY) ? -INFINITY : m_ref * c;
+        my_partial[row * mstride + DIM + 1] = l_sum;
+      }
+    }
+    if (DECODE && args.splits > 1) {
+      // ---- the block that arrives last merges the splits in order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) flag[1] = atomicAdd(&args.counters[tile_id], 1u) == (unsigned)args.splits - 1 ? 1u : 0u;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (flag[1]) {
+        __threadfence();
+        const float* all = args.partials + (size_t)tile_id * args.splits * group * mstride;
+        float* factor = reinterpret_cast<float*>(q_s);          // [splits][group], the query tile is done with
+        float* l_total = factor + (size_t)args.splits * group;
+        const int t = threadIdx.x - 64;
+        for (int i = t; i < args.splits * group; i += 128) factor[i] = all[(size_t)i * mstride + DIM];   // maxima first
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int r = t; r < group; r += 128) {
+          float m_all = -INFINITY;
+          for (int s2 = 0; s2 < args.splits; ++s2) m_all = fmaxf(m_all, factor[s2 * group + r]);
+          const float base = m_all == -INFINITY ? 0.f : m_all;
+          float l_all = 0.f;
+          for (int s2 = 0; s2 < args.splits; ++s2) {
+            const float f = fast_exp2(factor[s2 * group + r] - base);
+            l_all += all[((size_t)s2 * group + r) * mstride + DIM + 1] * f;
+            factor[s2 * group + r] = f;
+          }
+          l_total[r] = l_all;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int i = t; i < group * DIM; i += 128) {
+          const int r = i / DIM, col = i % DIM;
+          float acc = 0.f;
+#pragma unroll 8
+          for (int s2 = 0; s2 < args.splits; ++s2) acc += all[((size_t)s2 * group + r) * mstride + col] * factor[s2 * group + r];
+          args.out[((size_t)args.cu_q[seq] * args.q_heads + head + r) * DIM + col] = __float2bfloat16_rn(acc / l_total[r]);
+        }
+        if (threadIdx.x == 64) args.counters[tile_id] = 0;
+      }
+    }
+  }
+
+  // ---------------- teardown
+  fence_before_sync();
+  __syncthreads();
+  if (flag[0]) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies in flight land
+    __syncthreads();
+  }
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) != cudaSuccess ||
+        status != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }();
+  return fn;
+}
+
+void configure_once() {
+  static bool done = false;
+  if (done) return;
+  cudaFuncSetAttribute(attention_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaFuncSetAttribute(attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  done = true;
+}
+
+// q as a 2-D bf16 matrix [rows, cols] with rows `stride` elements apart: box 64 columns x 128 rows
+bool make_q_map(CUtensorMap* map, const void* q, long rows, long cols, long stride) {
+  auto encode = encode_fn();
+  if (!encode) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)stride * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)ROWS};
+  cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+// Whether the tensor-core kernel takes these sizes.
+LB_EXPORT int lb_attention_tcgen05_supports(int q_heads, int kv_heads, int dim, int page_tokens) {
+  return dim == DIM && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= ROWS && page_tokens >= 8 &&
+         page_tokens % 8 == 0 && KEYS % page_tokens == 0;
+}
+
+// The tensor map of one cache group's pool [planes = layers * 2, pages, kv_heads, page_tokens, dim]
+// (bf16, contiguous), written to `out` (128 bytes, 64-byte aligned storage is the caller's). One map
+// serves every layer and both K and V: the plane is a coordinate.
+LB_EXPORT int lb_attention_tcgen05_pool_map(void* out, const void* pool, long planes, long pages, int kv_heads,
+                                            int page_tokens, int dim) {
+  auto encode = encode_fn();
+  if (!encode || dim != DIM) return LB_ERR_SIZE;
+  if ((uintptr_t)pool % 16) return LB_ERR_ALIGN;
+  cuuint64_t dims[5] = {(cuuint64_t)dim, (cuuint64_t)page_tokens, (cuuint64_t)kv_heads, (cuuint64_t)pages, (cuuint64_t)planes};
+  cuuint64_t strides[4] = {(cuuint64_t)dim * 2, (cuuint64_t)page_tokens * dim * 2, (cuuint64_t)kv_heads * page_tokens * dim * 2,
+                           (cuuint64_t)pages * kv_heads * page_tokens * dim * 2};
+  cuuint32_t box[5] = {64, (cuuint32_t)page_tokens, 1, 1, 1};
+  cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  CUtensorMap map;
+  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(pool), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return LB_ERR_SIZE;
+  memcpy(out, &map, sizeof(map));
+  return 0;
+}
+
+LB_EXPORT int lb_attention_tcgen05_status() {
+  int code = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&code, g_attn_error, sizeof(int)) != cudaSuccess) return -100;
+  if (code) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+  return code;
+}
+
+// Prompt portions: tiles of 128 queries (tile_seq, tile_q0), grid (tiles, query heads).
+LB_EXPORT int lb_attention_tcgen05_prefill(const void* q, long q_rows, const void* pool_map, int layer, void* out,
+                                           const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
+                                           const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
+                                           int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!lb_attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens) || q_heads > 65535) return LB_ERR_SIZE;
+  if ((uintptr_t)q % 16) return LB_ERR_ALIGN;
+  configure_once();
+  CUtensorMap q_map, kv_map;
+  if (!make_q_map(&q_map, q, q_rows, (long)q_heads * dim, (long)q_heads * dim)) return LB_ERR_ALIGN;
+  memcpy(&kv_map, pool_map, sizeof(kv_map));
+  Args args{(bf16*)out, block_table, table_width, cu_q, ctx_len, tile_seq, tile_q0, q_heads, kv_heads, page_tokens, window,
+            2 * layer, scale * 1.4426950408889634f, 1, nullptr, nullptr};
+  const int code = lb_launch(attention_tcgen05_kernel<false>, dim3(n_tiles, q_heads), dim3(THREADS), (size_t)SMEM_BYTES,
+                             stream, q_map, kv_map, args);
+  return code ? code : lb_last_error();
+}
+
+// Sequences with one new token each, in order; grid (sequences, KV heads, splits).
+LB_EXPORT int lb_attention_tcgen05_decode(const void* q, long q_rows, const void* pool_map, int layer, void* out,
+                                          const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
+                                          int n_seqs, int q_heads, int kv_heads, int dim, int page_tokens, float scale,
+                                          int window, int splits, float* partials, long partial_floats, unsigned* counters,
+                                          int n_counters, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (!lb_attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens) || kv_heads > 65535 || splits < 1 || splits > 65535)
+    return LB_ERR_SIZE;
+  const int group = q_heads / kv_heads;
+  if (splits > 1 && (!partials || !counters || (long)n_seqs * q_heads * splits * (dim + 2) > partial_floats ||
+                     (long)n_seqs * kv_heads > n_counters || (size_t)(splits + 1) * group * sizeof(float) > TILE_BYTES))
+    return LB_ERR_SIZE;
+  if ((uintptr_t)q % 16) return LB_ERR_ALIGN;
+  configure_once();
+  CUtensorMap q_map, kv_map;
+  if (!make_q_map(&q_map, q, q_rows * q_heads, dim, dim)) return LB_ERR_ALIGN;
+  memcpy(&kv_map, pool_map, sizeof(kv_map));
+  Args args{(bf16*)out, block_table, table_width, cu_q, ctx_len, nullptr, nullptr, q_heads, kv_heads, page_tokens, window,
+            2 * layer, scale * 1.4426950408889634f, splits, partials, counters};
+  const int code = lb_launch(attention_tcgen05_kernel<true>, dim3(n_seqs, kv_heads, splits), dim3(THREADS),
+                             (size_t)SMEM_BYTES, stream, q_map, kv_map, args);
+  return code ? code : lb_last_error();
+}

@@ -32,6 +32,7 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "sampling": ("sampling.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),
     "attention_mma": ("attention_mma.cu", ()),
+    "attention_tcgen05": ("attention_tcgen05.cu", ()),
     "decode_attention_static": ("decode_attention_static.cu", ()),
 }
 

@@ -37,9 +37,9 @@ def _linear_swiglu_bf16(a: torch.Tensor, w_interleaved: torch.Tensor) -> torch.T
     return ops.swiglu(gate_up, out, block=ops.SWIGLU_BLOCK)
 
 
-def _attention_simt(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
+def _attention_simt(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
     tiles = batch.tiles[ops.attention_simt_block_queries()]
-    ops.attention_simt(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
+    ops.attention_simt(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
                        tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
 
 

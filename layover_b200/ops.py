@@ -229,7 +229,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None, seed_lo: torc
 
 
 # ------------------------------------------------------------------ the bfloat16 path
-BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_mma", "sampling")
+BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_mma", "attention_tcgen05", "sampling")
 
 _SCRATCH_FLOATS = 8 << 20     # split-K partial tiles (32 MiB)
 _SCRATCH_COUNTERS = 4096
@@ -381,20 +381,95 @@ def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, se
     return out
 
 
+# ---- attention on tcgen05 (head size 128, pages of 8..128 tokens dividing 128)
+TCGEN05_TILE = 128
+_pool_maps: dict[tuple, object] = {}
+
+
+def attention_tcgen05_supports(q_heads: int, kv_heads: int, dim: int, page_tokens: int) -> bool:
+    return (dim == 128 and kv_heads > 0 and q_heads % kv_heads == 0 and q_heads // kv_heads <= 128
+            and page_tokens >= 8 and page_tokens % 8 == 0 and 128 % page_tokens == 0)
+
+
+def _pool_map(pool: torch.Tensor):
+    """The TMA tensor map of a cache group's pool [layers, 2, pages, kv_heads, page_tokens, dim], made once."""
+    key = (pool.data_ptr(), tuple(pool.shape))
+    blob = _pool_maps.get(key)
+    if blob is None:
+        _need(pool, torch.bfloat16, "pool")
+        layers, two, pages, kv_heads, page_tokens, dim = pool.shape
+        blob = (ctypes.c_ubyte * 128)()
+        fn = _fn("attention_tcgen05", "lb_attention_tcgen05_pool_map", [c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int])
+        code = fn(ctypes.addressof(blob), _ptr(pool), layers * two, pages, kv_heads, page_tokens, dim)
+        if code:
+            raise ValueError(f"attention_tcgen05: cannot describe the pool to TMA ({_REFUSALS.get(code, code)})")
+        _pool_maps[key] = blob
+    return blob
+
+
+def attention_tcgen05_status() -> int:
+    """0, or which bounded wait of the tensor-core attention ran out. Synchronises; clears the code."""
+    lib = build.load("attention_tcgen05")
+    lib.lb_attention_tcgen05_status.restype = c_int
+    torch.cuda.synchronize()
+    return lib.lb_attention_tcgen05_status()
+
+
+def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, tile_seq, tile_q0, n_tiles, q_heads,
+                              kv_heads, dim, page_tokens, scale, window=0):
+    """Prompt portions on tcgen05: tiles of 128 queries; pool is the cache group's whole pool."""
+    for name, t in (("q", q), ("out", out)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len), ("tile_seq", tile_seq),
+                    ("tile_q0", tile_q0)):
+        _need(t, torch.int32, name)
+    fn = _fn("attention_tcgen05", "lb_attention_tcgen05_prefill",
+             [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 5 +
+             [c_float, c_int, c_void_p])
+    _check(fn(_ptr(q), q.shape[0], ctypes.addressof(_pool_map(pool)), int(layer), _ptr(out), _ptr(block_table),
+              block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads, kv_heads,
+              dim, page_tokens, float(scale), int(window), _stream()), "attention_tcgen05_prefill")
+    return out
+
+
+def attention_tcgen05_decode(q, pool, layer, out, block_table, cu_q, ctx_len, n_seqs, q_heads, kv_heads, dim,
+                             page_tokens, scale, window=0, splits=1):
+    """One new token per sequence on tcgen05, the context split `splits` ways."""
+    for name, t in (("q", q), ("out", out)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len)):
+        _need(t, torch.int32, name)
+    partials, counters = attention_scratch(q.device)
+    fn = _fn("attention_tcgen05", "lb_attention_tcgen05_decode",
+             [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 5 +
+             [c_float, c_int, c_int, c_void_p, c_long, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(q), q.shape[0], ctypes.addressof(_pool_map(pool)), int(layer), _ptr(out), _ptr(block_table),
+              block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale),
+              int(window), int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), _stream()),
+           "attention_tcgen05_decode")
+    return out
+
+
 def attention_bf16_tile_sizes() -> tuple[int, ...]:
-    return (attention_mma_block_queries(),)
+    return (attention_mma_block_queries(), TCGEN05_TILE)
 
 
-def attention_bf16(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
-    """The bfloat16 path's attention for one step: the split decode kernel when every sequence brings a
-    single token, else the tile kernel over the step's query tiles."""
+def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
+    """The bfloat16 path's attention for one step: prompt portions go through the tcgen05 tile kernel
+    where it takes the sizes (head size 128, pages of 8..128 tokens), else through the mma.sync
+    one; steps of single tokens go through the split decode kernel."""
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
         # the widest context the block table can describe (what a captured step may later see)
         splits = decode_splits(batch.n_seqs, q_heads, kv_heads, dim, block_table.shape[1] * page_tokens, sms)
-        attention_decode_bf16(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, None, batch.n_seqs,
-                              q_heads, kv_heads, dim, page_tokens, scale, window, splits)
+        attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, None,
+                              batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits)
+        return
+    if cache.pool is not None and attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens):
+        tiles = batch.tiles[TCGEN05_TILE]
+        attention_tcgen05_prefill(q, cache.pool, cache.layer, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq,
+                                  tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
         return
     tiles = batch.tiles[attention_mma_block_queries()]
-    attention_prefill_bf16(q, k_pool, v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
-                           tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
+    attention_prefill_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq,
+                           tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)

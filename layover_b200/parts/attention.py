@@ -109,8 +109,8 @@ class Attention(Part):
         return self.runtime.linear(out, self.w_o)
 
     def attend(self, q, cache, batch, group, out) -> None:
-        self.runtime.attention(q, cache.k_pool, cache.v_pool, out, group.block_table, batch, self.q_heads,
-                               self.kv_heads, self.dim, cache.page_tokens, self.scale, self.window or 0)
+        self.runtime.attention(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim,
+                               cache.page_tokens, self.scale, self.window or 0)
 
 
 def attention_spec(hidden, q_heads, kv_heads, head_dim, qk_norm_eps, theta, window=None, shares_cache=False) -> PartSpec:

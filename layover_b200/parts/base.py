@@ -62,7 +62,7 @@ class Runtime:
     dtype: torch.dtype
     device: torch.device
     linear: Callable[..., torch.Tensor]   # linear(a [M, K], w [N, K], out_dtype=None) -> [M, N]
-    # attention(q, k_pool, v_pool, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window)
+    # attention(q, cache_view, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window)
     attention: Callable[..., None] | None = None
     # linear_swiglu(a, w_interleaved) -> silu(gate) * up or None; w made by interleave_gate_up(gate, up)
     linear_swiglu: Callable[..., torch.Tensor | None] | None = None

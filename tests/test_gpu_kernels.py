@@ -430,3 +430,90 @@ def test_gemm_tcgen05_swiglu_epilogue(m, inter, k):
         close(out, expected, torch.bfloat16)
     with pytest.raises(ValueError, match="swiglu"):
         o.gemm_tcgen05(a, w[:2 * inter - 64], torch.empty(m, inter - 32, device="cuda", dtype=torch.bfloat16), epilogue="swiglu")
+
+
+def run_tc_attention(lengths, q_lens, q_heads, kv_heads, page, window=0, seed=0, decode=False, splits=1, layers=3, layer=1):
+    """The tcgen05 kernels against the plain attention: the pool has several layers and both planes,
+    as the cache manager lays it out, and only plane (layer, K / V) holds the data."""
+    o = ops()
+    dim = 128
+    k_pool, v_pool, table, ks, vs = paged_setup(torch.bfloat16, lengths, kv_heads, dim, page, seed)
+    pages = k_pool.shape[0]
+    pool = torch.full((layers, 2, pages, kv_heads, page, dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    pool[layer, 0], pool[layer, 1] = k_pool, v_pool
+    gen = torch.Generator().manual_seed(seed + 1)
+    qs = [torch.randn(n, q_heads, dim, generator=gen).to(torch.bfloat16) for n in q_lens]
+    q = torch.cat(qs).reshape(-1, q_heads * dim).cuda()
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    scale = 1.0 / math.sqrt(dim)
+    if decode:
+        o.attention_tcgen05_decode(q, pool, layer, out, table, cu, ctx, len(lengths), q_heads, kv_heads, dim, page, scale,
+                                   window, splits)
+    else:
+        tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, 128)]
+        tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+        tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+        o.attention_tcgen05_prefill(q, pool, layer, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads,
+                                    dim, page, scale, window)
+    assert o.attention_tcgen05_status() == 0
+    expected = []
+    for s, n in enumerate(lengths):
+        full_q = torch.zeros(n, q_heads, dim, dtype=torch.bfloat16)
+        full_q[n - q_lens[s]:] = qs[s]
+        expected.append(plain_attention(full_q, ks[s], vs[s], window or None)[n - q_lens[s]:])
+    return out.cpu().view(-1, q_heads, dim), torch.cat(expected)
+
+
+@pytest.mark.parametrize("q_heads, kv_heads, page", [(4, 1, 16), (2, 2, 8), (32, 8, 16), (3, 1, 32), (8, 2, 128)])
+def test_attention_tcgen05_prefill(q_heads, kv_heads, page):
+    lengths = [37, 300, 128, 129, 127, 1, 65, 256, 700]
+    q_lens = [37, 129, 128, 1, 127, 1, 2, 256, 300]
+    for _ in range(2):
+        got, expected = run_tc_attention(lengths, q_lens, q_heads, kv_heads, page)
+        assert not torch.isnan(got).any()              # NaN in unused slots, pages and planes did not leak
+        close(got, expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("window", [1, 5, 128, 200])
+def test_attention_tcgen05_prefill_window(window):
+    got, expected = run_tc_attention([270, 440, 33], [270, 3, 1], 4, 2, 16, window=window)
+    close(got, expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("q_heads, kv_heads, page", [(4, 1, 16), (32, 8, 16), (16, 1, 8), (6, 6, 32)])
+def test_attention_tcgen05_decode(q_heads, kv_heads, page, splits):
+    lengths = [1, 2, page, page + 1, 127, 128, 129, 255, 256, 257, 700, 1000]
+    for _ in range(2):
+        got, expected = run_tc_attention(lengths, [1] * len(lengths), q_heads, kv_heads, page, decode=True, splits=splits)
+        assert not torch.isnan(got).any()
+        close(got, expected, torch.bfloat16)
+
+
+def test_attention_tcgen05_scores_far_apart_force_rescaling():
+    """Keys whose scores grow along the sequence make the running maximum jump by far more than the
+    2^8 that the kernel tolerates before it rescales its accumulated output."""
+    o = ops()
+    dim, n, page = 128, 640, 16
+    gen = torch.Generator().manual_seed(9)
+    direction = torch.randn(dim, generator=gen)
+    direction /= direction.norm()
+    k_pool, v_pool, table, ks, vs = paged_setup(torch.bfloat16, [n], 1, dim, page, seed=5, poison=False)
+    for key in range(n):                                       # key j scores about j / 8 in natural units
+        k = (direction * (key / 8.0) * math.sqrt(dim) / 10.0).to(torch.bfloat16)
+        k_pool[int(table[0, key // page]), 0, key % page] = k.cuda()
+        ks[0][key, 0] = k
+    q = (direction * 10.0).to(torch.bfloat16).view(1, 1, dim).repeat(n, 1, 1)
+    pool = torch.stack((k_pool, v_pool))[None].contiguous()
+    qf = q.reshape(n, dim).cuda()
+    out = torch.empty_like(qf)
+    cu = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+    ctx = torch.tensor([n], dtype=torch.int32, device="cuda")
+    tiles = list(range(0, n, 128))
+    o.attention_tcgen05_prefill(qf, pool, 0, out, table, cu, ctx, torch.zeros(len(tiles), dtype=torch.int32, device="cuda"),
+                                torch.tensor(tiles, dtype=torch.int32, device="cuda"), len(tiles), 1, 1, dim, page, 1 / math.sqrt(dim))
+    assert o.attention_tcgen05_status() == 0
+    expected = plain_attention(q, ks[0], vs[0])
+    close(out.cpu().view(n, 1, dim), expected, torch.bfloat16)
