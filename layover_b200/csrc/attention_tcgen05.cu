@@ -204,9 +204,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     q_row = args.cu_q[seq] * args.q_heads + head;     // row of q viewed as [tokens * heads, dim]
     n_rows = group;
   } else {
-    seq = args.tile_seq[blockIdx.x];
-    const int q0 = args.tile_q0[blockIdx.x];
-    head = blockIdx.y; kv_head = head / group;
+    // heads run fastest and the tile list is walked backwards: within a sequence later tiles have
+    // more keys to visit, and the longest jobs should start first
+    const int tile_index = gridDim.y - 1 - blockIdx.y;
+    seq = args.tile_seq[tile_index];
+    const int q0 = args.tile_q0[tile_index];
+    head = blockIdx.x; kv_head = head / group;
     const int row0 = args.cu_q[seq], q_len = args.cu_q[seq + 1] - row0, ctx = args.ctx_len[seq];
     n_rows = min(ROWS, q_len - q0);
     p_first = ctx - q_len + q0; p_last = p_first + n_rows - 1;
@@ -351,42 +354,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       // loads and stores are warp-wide), every lane by its own factor.
       const bool grow = (tile_max - m_ref) * c > RESCALE_THRESHOLD || (m_ref == -INFINITY && tile_max > -INFINITY);
       const bool any_grow = __any_sync(0xffffffffu, grow);
-      // the previous tile's second product must be done before P is overwritten or O is touched
+      // The exponentials need only the reference maximum, so they are taken before waiting for the
+      // previous tile's second product; that product must be done before the probabilities in
+      // shared memory are overwritten or the output is touched.
+      const float m_new = grow ? tile_max : m_ref;
+      const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * c);
+      const float neg_base = (m_new == -INFINITY) ? 0.f : -m_new * c;
+      uint32_t w[KEYS / 2];
+      float tile_sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < KEYS / 2; ++e) {
+        const float a = fast_exp2(fmaf(s[2 * e], c, neg_base));
+        const float b = fast_exp2(fmaf(s[2 * e + 1], c, neg_base));
+        tile_sum += a + b;
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+        w[e] = *reinterpret_cast<const uint32_t*>(&pair);
+      }
+      l_sum = l_sum * factor + tile_sum;
+      m_ref = m_new;
       if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) { atomicCAS(&g_attn_error, 0, 6); flag[0] = 1; ok = false; break; }
       fence_after_sync();
-      if (any_grow) {
-        const float m_new = grow ? tile_max : m_ref;
-        const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * c);
-        if (i > 0) {
+      if (any_grow && i > 0) {
 #pragma unroll
-          for (int ch = 0; ch < DIM / 16; ++ch) {
-            float v[16];
-            tmem_ld16(tmem_o + lane_addr + ch * 16, v);
+        for (int ch = 0; ch < DIM / 16; ++ch) {
+          float v[16];
+          tmem_ld16(tmem_o + lane_addr + ch * 16, v);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) v[e] *= factor;
-            tmem_st16(tmem_o + lane_addr + ch * 16, v);
-          }
+          for (int e = 0; e < 16; ++e) v[e] *= factor;
+          tmem_st16(tmem_o + lane_addr + ch * 16, v);
         }
-        l_sum *= factor;
-        m_ref = m_new;
       }
-      const float neg_base = (m_ref == -INFINITY) ? 0.f : -m_ref * c;
       // probabilities as bf16 into the A operand of the second product: row `row`, 16-byte pieces
       // of 8 keys, swizzled like every 128-byte row
 #pragma unroll
       for (int piece = 0; piece < KEYS / 8; ++piece) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = fast_exp2(fmaf(s[piece * 8 + 2 * e], c, neg_base));
-          const float b = fast_exp2(fmaf(s[piece * 8 + 2 * e + 1], c, neg_base));
-          l_sum += a + b;
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
-          w[e] = *reinterpret_cast<const uint32_t*>(&pair);
-        }
         const int half = piece >> 3, chunk = piece & 7;
         uint8_t* dst = p_s + half * HALF_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
-        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[4 * piece], w[4 * piece + 1], w[4 * piece + 2], w[4 * piece + 3]);
       }
       // V rows of keys that are not part of the context may hold anything (a stale or poisoned
       // page): zero them, since 0 x NaN would still be NaN. Only boundary tiles have such rows.
@@ -577,13 +581,13 @@ LB_EXPORT int lb_attention_tcgen05_status() {
   return code;
 }
 
-// Prompt portions: tiles of 128 queries (tile_seq, tile_q0), grid (tiles, query heads).
+// Prompt portions: tiles of 128 queries (tile_seq, tile_q0), grid (query heads, tiles).
 LB_EXPORT int lb_attention_tcgen05_prefill(const void* q, long q_rows, const void* pool_map, int layer, void* out,
                                            const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                            const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
                                            int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (!lb_attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens) || q_heads > 65535) return LB_ERR_SIZE;
+  if (!lb_attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens) || n_tiles > 65535) return LB_ERR_SIZE;
   if ((uintptr_t)q % 16) return LB_ERR_ALIGN;
   configure_once();
   CUtensorMap q_map, kv_map;
@@ -591,7 +595,7 @@ LB_EXPORT int lb_attention_tcgen05_prefill(const void* q, long q_rows, const voi
   memcpy(&kv_map, pool_map, sizeof(kv_map));
   Args args{(bf16*)out, block_table, table_width, cu_q, ctx_len, tile_seq, tile_q0, q_heads, kv_heads, page_tokens, window,
             2 * layer, scale * 1.4426950408889634f, 1, nullptr, nullptr};
-  const int code = lb_launch(attention_tcgen05_kernel<false>, dim3(n_tiles, q_heads), dim3(THREADS), (size_t)SMEM_BYTES,
+  const int code = lb_launch(attention_tcgen05_kernel<false>, dim3(q_heads, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES,
                              stream, q_map, kv_map, args);
   return code ? code : lb_last_error();
 }
