@@ -192,14 +192,18 @@ def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
 
     vocab = model.spec.vocab_size
     start = max(1, (PROMPT + CONTEXT) // 2 - steps // 2 - warmup)
-    pages = batch * (-(-(start + warmup + steps + 2) // PAGE))
+    # requests that finish their prompt early decode while the others still prefill: leave room for
+    # those tokens, so that every request is still running at the end of the timed steps
+    slack = batch * (-(-start // PREFILL_TOKENS)) + 8
+    budget = warmup + steps + slack
+    pages = batch * (-(-(start + budget + 1) // PAGE))
     cache = lb.PagedKVCache(model, pages, block_tokens=PAGE, max_requests=batch)
     engine = lb.Engine(model, cache, lb.EngineConfig(batch, PREFILL_TOKENS, PREFILL_TOKENS), cuda_graphs=True)
     engine.step_fn.graph_sizes = (batch,)
     engine.step_fn.graph_table_width = cache.blocks_for(CONTEXT)
     for i in range(batch):
         prompt = torch.randint(0, vocab, (start,), generator=gen).tolist()
-        engine.add_request(lb.Request(str(i), prompt, warmup + steps + 1))
+        engine.add_request(lb.Request(str(i), prompt, budget))
     while any(r.state is not lb.State.DECODE for r in engine.running) or engine.waiting:
         engine.step()
     for _ in range(warmup):
@@ -211,7 +215,9 @@ def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
         engine.step()
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - began
-    produced = sum(len(r.generated) for r in engine.running + engine.finished) - produced
+    if len(engine.running) != batch:
+        raise RuntimeError("a request finished inside the timed steps: the end-to-end number would be wrong")
+    produced = sum(len(r.generated) for r in engine.running) - produced
     width = engine.step_fn.graph_table_width
     h2d = 4 * lb.engine.BatchBuilder.buffer_size(lb.engine.BatchCapacity(batch, width), len(cache.paged), model.tile_sizes())
     return {"value": produced / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
@@ -378,7 +384,8 @@ def run_reference(args) -> dict:
         pass
     batch, steps, warmup = args.batch, args.steps, args.warmup
     start = max(1, (PROMPT + CONTEXT) // 2 - steps // 2 - warmup)
-    blocks = batch * (-(-(start + warmup + steps + 2) // PAGE)) + 2
+    slack = batch * (-(-start // PREFILL_TOKENS)) + 8      # tokens decoded while other prompts still prefill
+    blocks = batch * (-(-(start + warmup + steps + slack + 2) // PAGE)) + 2
     cache = PagedKVCache(cfg, blocks, "cuda", torch.bfloat16, PAGE)
     graphs = False
     if backend == "triton" and batch <= 8:
@@ -391,7 +398,8 @@ def run_reference(args) -> dict:
     engine = Engine(model, cache, EngineConfig(batch, PREFILL_TOKENS, PREFILL_TOKENS))
     gen = torch.Generator().manual_seed(0)
     for i in range(batch):
-        engine.add_request(Request(str(i), torch.randint(0, cfg.vocab_size, (start,), generator=gen).tolist(), warmup + steps + 2))
+        engine.add_request(Request(str(i), torch.randint(0, cfg.vocab_size, (start,), generator=gen).tolist(),
+                                   warmup + steps + slack))
     clocks = ClockSampler()
     try:
         while engine.waiting or any(r.state is not State.DECODE for r in engine.running):
