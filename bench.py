@@ -186,7 +186,8 @@ def prefill_flops(cfg, layers: int, tokens: int) -> float:
 
 
 def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
-    """Through the public entry point: requests with host token ids, tokens read back every step."""
+    """Through the public entry point: requests with host token ids, tokens read back every step
+    (pipelined stepping: each call launches a step and takes in the tokens of the one before)."""
     import torch
     import layover_b200 as lb
 
@@ -207,12 +208,12 @@ def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
     while any(r.state is not lb.State.DECODE for r in engine.running) or engine.waiting:
         engine.step()
     for _ in range(warmup):
-        engine.step()
+        engine.step_pipelined()
     torch.cuda.synchronize()
     produced = sum(len(r.generated) for r in engine.running)
     began = time.perf_counter()
     for _ in range(steps):
-        engine.step()
+        engine.step_pipelined()      # launches one step and reads the tokens of the one before it
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - began
     if len(engine.running) != batch:

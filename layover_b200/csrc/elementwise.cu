@@ -28,6 +28,23 @@ LB_EXPORT int lb_embed(int dtype, const int* ids, const void* table, void* x, in
   return lb_last_error();
 }
 
+// ---------------------------------------------------------------- tokens that are still on the device
+// ids[t] = previous[source[t]] where source[t] >= 0: a step may be launched before the host has read
+// the tokens that the step before it sampled; those rows take their token from the sampler's output.
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ previous,
+                                    int tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < tokens && source[t] >= 0) ids[t] = previous[source[t]];
+}
+
+LB_EXPORT int lb_patch_tokens(int* ids, const int* source, const int* previous, int tokens, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  lb_launch(patch_tokens_kernel, (tokens + 127) / 128, 128, 0, stream, ids, source, previous, tokens);
+  return lb_last_error();
+}
+
 // ---------------------------------------------------------------- add + RMSNorm
 // v = x[row] + delta[row] (sum in 32-bit, rounded to T once; written back to x unless rows are
 // picked), out = weight * round_T(v * rsqrt(mean(v^2) + eps))   (layover/model.py:31-36,165-166)

@@ -9,6 +9,7 @@ side; the tokens of all entries are laid end to end:
   ctx_len [S]                         the request's length once this step's tokens are in
   state_slots [S]                     the request's slot of fixed-size state
   logit_rows [R]                      flat rows whose logits are returned, in entry / want order
+  token_src [T]                       row of the previous step's sampled tokens a token comes from, or -1
   per paged cache group:
     block_table [S, W]                page ids, padded with the group's scratch page
     slot_map [T]                      page * page_tokens + slot where the token's K and V go
@@ -33,6 +34,8 @@ from ..cache.manager import CacheManager, SequenceCache
 
 @dataclass
 class StepEntry:
+    """`tokens` are token ids; a negative value -(k + 1) stands for "row k of the tokens that the
+    previous step sampled", which are still on the device when this step is launched."""
     seq: SequenceCache
     tokens: list[int]
     want: list[int] = field(default_factory=list)
@@ -62,6 +65,8 @@ class StepBatch:
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
     n_logit_rows: int
+    token_src: torch.Tensor      # per token: row of the previous step's sampled tokens, or -1
+    device_tokens: bool          # whether any token comes from the device
     groups: list[GroupBatch]
     tiles: dict[int, QueryTiles]
     # host-side facts for planning launches
@@ -142,7 +147,7 @@ class BatchBuilder:
         layout = _Layout()
         layout.add("token_ids", n_tokens); layout.add("positions", n_tokens)
         layout.add("cu_q", n_seqs + 1); layout.add("ctx_len", n_seqs); layout.add("state_slots", n_seqs)
-        layout.add("logit_rows", n_rows)
+        layout.add("logit_rows", n_rows); layout.add("token_src", n_tokens)
         for g in range(len(cache.paged)):
             layout.add(f"table{g}", n_seqs, width); layout.add(f"slots{g}", n_tokens)
         tile_lists = {}
@@ -172,6 +177,10 @@ class BatchBuilder:
             tokens_flat.append(0); positions.append(0); cu.append(cu[-1] + 1)
         if capacity:
             rows = list(range(n_seqs))
+        device_tokens = any(t < 0 for t in tokens_flat)
+        put("token_src", [-t - 1 if t < 0 else -1 for t in tokens_flat] if device_tokens else [-1] * n_tokens)
+        if device_tokens:
+            tokens_flat = [max(t, 0) for t in tokens_flat]
         put("token_ids", tokens_flat); put("positions", positions); put("cu_q", cu); put("ctx_len", ctx_lens)
         put("state_slots", [e.seq.slot for e in entries] + [cache.scratch_slot] * (n_seqs - real))
         put("logit_rows", rows)
@@ -222,6 +231,7 @@ class BatchBuilder:
             n_tokens=n_tokens, n_seqs=n_seqs,
             token_ids=get("token_ids"), positions=get("positions"), cu_q=get("cu_q"), ctx_len=get("ctx_len"),
             state_slots=get("state_slots"), logit_rows=get("logit_rows"), n_logit_rows=n_rows,
+            token_src=get("token_src"), device_tokens=device_tokens,
             groups=[GroupBatch(get(f"table{g}"), get(f"slots{g}")) for g in range(len(cache.paged))],
             tiles={size: QueryTiles(get(f"tile_seq{size}"), get(f"tile_q0{size}"), len(tiles))
                    for size, tiles in tile_lists.items()},
@@ -234,7 +244,7 @@ class BatchBuilder:
         """Upper bound of the int32 words a fixed-capacity batch takes."""
         pad = lambda n: -(-max(n, 1) // 4) * 4
         s = capacity.seqs
-        total = 2 * pad(s) + pad(s + 1) + 3 * pad(s)
+        total = 3 * pad(s) + pad(s + 1) + 3 * pad(s)
         total += n_groups * (pad(s * capacity.table_width) + pad(s))
         total += len(set(tile_sizes)) * 2 * pad(s)
         return total

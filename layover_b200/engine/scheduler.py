@@ -12,6 +12,14 @@ come, first served) and a request that could never fit is refused when it is add
 (layover/engine.py:91-132). An `OutOfBlocks` that reaches `step()` is therefore a bug, not a
 state.
 
+Pipelined stepping (`step_pipelined`, used by `run_until_idle` with the real sampler): a step is
+launched before the host has read the tokens of the step before it. Which requests decode next
+does not depend on the token values (finishing by `max_new_tokens` is a count), only the token
+ids do, and those the next step reads on the device, straight from the sampler's output. The
+host then reads the previous step's tokens while the GPU already runs the next step, so the
+scheduler, the batch building and the copies cost no GPU time. A request that ends on a stop
+token is found out one step late: it has one more step in flight, whose token is dropped.
+
 Differences from the reference, on purpose: a step is ONE batch (prompt portions and decoded
 tokens together) instead of one call per prefilling request followed by a decode call; the
 first token of a request is sampled from the last row of its prompt and the request joins the
@@ -57,6 +65,7 @@ class Request:
     finished_at: float | None = None
     error: str | None = None
     cache: object = None   # the cache manager's record of this request while it runs
+    pending: int = 0       # tokens sampled for it that the host has not read yet (pipelined stepping)
 
     @property
     def max_tokens(self) -> int:
@@ -96,7 +105,8 @@ class Engine:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self.finished: list[Request] = []
-        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "largest_batch": 0}
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "largest_batch": 0, "dropped_tokens": 0}
+        self._inflight = None      # (requests sampled by the step in flight, its PendingTokens)
 
     # ------------------------------------------------------------------ admission
     def add_request(self, request: Request) -> None:
@@ -216,10 +226,74 @@ class Engine:
         self.running = still_running
         return retired
 
+    # ------------------------------------------------------------------ pipelined stepping
+    def step_pipelined(self) -> bool:
+        """Launch the next step, then take in the tokens of the step before it."""
+        self._admit()
+        previous = self._inflight
+        source = {id(r): row for row, r in enumerate(previous[0])} if previous else {}
+        plan = []
+        for request in self.running:
+            if request.state is State.DECODE and len(request.generated) + request.pending < request.max_new_tokens \
+                    and not (request.pending == 0 and request.done):
+                # its newest token: still on the device (row of the step in flight) or already here
+                token = -(source[id(request)] + 1) if request.pending else request.generated[-1]
+                plan.append((request, [token], True))
+        budget = self.config.prefill_budget
+        for request in self.running:
+            if request.state is not State.PREFILL or budget <= 0:
+                continue
+            count = min(self.config.prefill_chunk, budget, len(request.prompt) - request.prefilled)
+            tokens = request.prompt[request.prefilled: request.prefilled + count]
+            budget -= count
+            plan.append((request, tokens, request.prefilled + count == len(request.prompt)))
+        launched = None
+        if plan:
+            entries = [StepEntry(r.cache, tokens, [len(tokens) - 1] if sample else []) for r, tokens, sample in plan]
+            logits = self.step_fn(entries, previous[1].device if previous else None)
+            sampled = [r for r, _, sample in plan if sample]
+            pending = self.sampler.launch(logits, [SamplingParams(r.temperature, r.seed) for r in sampled],
+                                          [len(r.generated) + r.pending for r in sampled])
+            for request, new_tokens, _ in plan:
+                if request.state is State.PREFILL:
+                    request.prefilled += len(new_tokens)
+                    self.stats["prefill_tokens"] += len(new_tokens)
+                    if request.prefilled == len(request.prompt):
+                        request.state = State.DECODE          # its first token is on its way
+                else:
+                    self.stats["decode_tokens"] += 1
+            for request in sampled:
+                request.pending += 1
+            launched = (sampled, pending)
+            self.stats["steps"] += 1
+            self.stats["largest_batch"] = max(self.stats["largest_batch"], len(plan))
+        retired = False
+        if previous is not None:
+            retired = self._take_in(previous)
+        self._inflight = launched
+        return bool(plan) or retired or previous is not None
+
+    def _take_in(self, step) -> bool:
+        """Read a launched step's tokens and hand them to their requests."""
+        sampled, pending = step
+        for request, token in zip(sampled, pending.result()):
+            request.pending -= 1
+            if request.state is State.FINISHED:        # ended on a stop token one step earlier
+                self.stats["dropped_tokens"] += 1
+                continue
+            request.generated.append(int(token))
+            if request.first_token_at is None:
+                request.first_token_at = self.clock()
+            if request.on_token is not None:
+                request.on_token(request, int(token))
+        return self._retire()
+
     def run_until_idle(self, max_steps: int = 1_000_000) -> list[Request]:
+        pipelined = hasattr(self.sampler, "launch")
         for _ in range(max_steps):
-            if self.idle:
+            if self.idle and self._inflight is None:
                 return self.finished
-            if not self.step() and self.waiting and not self.running:
+            progressed = self.step_pipelined() if pipelined else self.step()
+            if not progressed and self.waiting and not self.running:
                 raise RuntimeError("the head request can never be admitted")
         raise RuntimeError("engine did not become idle")

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..profiling import nvtx_range
 from .batch import BatchBuilder, BatchCapacity, StepBatch, StepEntry
@@ -42,7 +43,6 @@ class _DecodeGraph:
             for _ in range(2):
                 step.model.forward(batch, step.cache)
         torch.cuda.current_stream().wait_stream(side)
-        from .. import ops
         self.graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
         with torch.cuda.graph(self.graph, pool=pool):
@@ -70,7 +70,7 @@ class StepFunction:
         self.replayed_launches = 0
 
     # ---- checks the kernels cannot make
-    def _check(self, entries: list[StepEntry]) -> None:
+    def _check(self, entries: list[StepEntry], previous_rows: int = 0) -> None:
         seen = set()
         for entry in entries:
             seq = entry.seq
@@ -84,7 +84,7 @@ class StepFunction:
             if seq.num_tokens + len(entry.tokens) > self.max_position:
                 raise ValueError(f"request {seq.request_id!r} would exceed {self.max_position} positions")
             for token in entry.tokens:
-                if not 0 <= token < self.vocab_size:
+                if not -previous_rows <= token < self.vocab_size:
                     raise ValueError(f"request {seq.request_id!r}: token {token} is outside the vocabulary")
 
     def _reserve(self, entries: list[StepEntry]) -> None:
@@ -102,17 +102,21 @@ class StepFunction:
             cache.grow(entry.seq, entry.seq.num_tokens + len(entry.tokens))
 
     # ---- the step
-    def __call__(self, entries: list[StepEntry]) -> torch.Tensor:
+    def __call__(self, entries: list[StepEntry], previous_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [wanted rows, vocab] in 32-bit on the device, in the order of entries and want.
 
+        `previous_tokens` (int32, on the device) are the tokens the step before sampled; entries name
+        them with negative token values, so a step can be launched before the host has read them.
         After a replayed graph the result is a view of the graph's output, which the next replay
         of the same bucket overwrites: use it (sample, copy) before the next step."""
-        self._check(entries)
+        self._check(entries, 0 if previous_tokens is None else previous_tokens.shape[0])
         self._reserve(entries)
         with nvtx_range("step"):
             graph = self._graph_for(entries)
             if graph is not None:
                 batch = self.builder.build(entries, graph.capacity, graph.buffer)
+                if batch.device_tokens:
+                    ops.patch_tokens(batch.token_ids, batch.token_src, previous_tokens)
                 graph.graph.replay()
                 self.graph_replays += 1
                 self.replayed_launches += graph.launches
@@ -120,6 +124,8 @@ class StepFunction:
                 logits = graph.logits[: len(entries)] if len(rows) == len(entries) else graph.logits[rows]
             else:
                 batch = self.builder.build(entries)
+                if batch.device_tokens:
+                    ops.patch_tokens(batch.token_ids, batch.token_src, previous_tokens)
                 logits = self.model.forward(batch, self.cache)
         for entry in entries:
             self.cache.commit(entry.seq, entry.seq.num_tokens + len(entry.tokens))

@@ -87,6 +87,13 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
+def patch_tokens(ids: torch.Tensor, source: torch.Tensor, previous: torch.Tensor) -> None:
+    """ids[t] = previous[source[t]] where source[t] >= 0 (tokens sampled by a step the host has not read yet)."""
+    _need(ids, torch.int32, "ids"); _need(source, torch.int32, "source"); _need(previous, torch.int32, "previous")
+    fn = _fn("elementwise", "lb_patch_tokens", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(ids), _ptr(source), _ptr(previous), ids.shape[0], _stream()), "patch_tokens")
+
+
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
     """x += delta (in place, unless `rows` picks source rows), out = rmsnorm(x) * weight.

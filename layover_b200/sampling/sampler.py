@@ -31,9 +31,14 @@ class Sampler:
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams], steps: list[int]) -> list[int]:
         """One token per row of `logits` [R, V]; `steps[r]` is how many tokens row r's request has
         sampled before this one. One copy in, one copy out."""
+        return self.launch(logits, params, steps).result()
+
+    def launch(self, logits: torch.Tensor, params: list[SamplingParams], steps: list[int]) -> "PendingTokens":
+        """Sample without waiting: the tokens stay on the device (the next step may read them
+        there) and travel to pinned host memory behind the kernel; `result()` waits for them."""
         rows = logits.shape[0]
         if rows == 0:
-            return []
+            return PendingTokens(None, None, None)
         if len(params) != rows or len(steps) != rows:
             raise ValueError("one SamplingParams and one step count per row of logits")
         tokens = torch.empty(rows, dtype=torch.int32, device=self.device)
@@ -47,7 +52,24 @@ class Sampler:
             host[3] = torch.tensor([_signed(s & 0xFFFFFFFF) for s in steps], dtype=torch.int32)
             dev = host.to(self.device, non_blocking=True)
             ops.sample(logits, dev[0].view(torch.float32), dev[1], dev[2], dev[3], tokens)
-        return tokens.tolist()
+        host = torch.empty(rows, dtype=torch.int32, pin_memory=True)
+        host.copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(tokens, host, event)
+
+
+class PendingTokens:
+    """Sampled tokens on their way to the host."""
+
+    def __init__(self, device, host, event):
+        self.device, self._host, self._event = device, host, event
+
+    def result(self) -> list[int]:
+        if self._host is None:
+            return []
+        self._event.synchronize()
+        return self._host.tolist()
 
 
 def _signed(word: int) -> int:

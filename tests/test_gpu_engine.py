@@ -74,6 +74,38 @@ def test_temperature_sampling_is_the_plain_rule_and_ignores_the_batch(tiny_folde
     assert together != lb.generate(model, prompts, max_new_tokens=24, temperature=0.8, seed=6, block_tokens=16, config=config)
 
 
+def test_pipelined_stepping_equals_step_by_step_and_handles_stop_tokens(tiny_folders, models):
+    """`run_until_idle` launches each step before it has read the tokens of the one before; `step`
+    waits for its own tokens. Both must give the plain implementation's tokens, also when a request
+    ends on a stop token (found out one step late, with one token in flight that is dropped)."""
+    _, raw, weights = tiny_folders["b"]
+    model = models("b", "fp32")
+    prompts = [random_prompt(512, n, 300 + n) for n in (3, 20, 70, 9)]
+    expected = [plain_generate(raw, weights, p, 12) for p in prompts]
+    stops = [frozenset({expected[0][4]}), frozenset(), frozenset({expected[2][0]}), frozenset({expected[3][11]})]
+    cut = []
+    for tokens, stop in zip(expected, stops):
+        end = next((i for i, t in enumerate(tokens) if t in stop), len(tokens) - 1)
+        cut.append(tokens[:end + 1])
+    for pipelined in (True, False):
+        for graphs in (False, True):
+            cache = lb.PagedKVCache(model, 64, block_tokens=16, max_requests=4)
+            engine = lb.Engine(model, cache, lb.EngineConfig(max_batch=3, prefill_chunk=16, prefill_budget=24), cuda_graphs=graphs)
+            for i, (p, stop) in enumerate(zip(prompts, stops)):
+                engine.add_request(lb.Request(str(i), p, 12, stop))
+            if pipelined:
+                engine.run_until_idle()
+            else:
+                while not engine.idle:
+                    engine.step()
+            done = {r.request_id: r.generated for r in engine.finished}
+            assert [done[str(i)] for i in range(4)] == cut
+            assert cache.num_free == 64 and all(r.pending == 0 for r in engine.finished)
+            cache.check()
+            if pipelined:
+                assert engine.stats["dropped_tokens"] >= 1      # the steps in flight behind the stop tokens
+
+
 def test_long_decoding_and_page_reuse(tiny_folders, models):
     _, raw, weights = tiny_folders["a"]
     model = models("a", "fp32")
