@@ -199,7 +199,7 @@ LB_EXPORT int lb_rope_table(const int* positions, const float* inv_freq, float* 
 
 // ---------------------------------------------------------------- QK-norm + rotary + KV write
 // One warp per (token, head) of the fused projection row [q heads | k heads | v heads] x dim
-// (dim a multiple of 8, up to 256; rows, outputs and pages 16-byte aligned).
+// (dim a multiple of 16; rows, outputs and pages 16-byte aligned).
 //   q, k: per-head RMSNorm over dim (weight shared by the heads, layover/model.py:124-125), then
 //         x*cos + rotate_half(x)*sin with cos/sin from the step's table, rounded to T
 //         (layover/model.py:100-102,127-128,193-197); dims >= 2*n_freq pass through unrotated.
@@ -209,30 +209,9 @@ LB_EXPORT int lb_rope_table(const int* positions, const float* inv_freq, float* 
 // Null norm weights skip the norm, a null table skips the rotation, null pools skip the write
 // (then k is written back in place into the projection row, for a position encoding that runs
 // as a separate step), a null q_out skips the q heads (the pass that only writes pages).
-// four elements of each half per lane (dim <= 256), one 8- or 16-byte access each
-template <typename T> struct Quad;
-template <> struct Quad<float> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { Pack<float>::load(p, v); }
-  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { Pack<float>::store(p, v); }
-};
-template <> struct Quad<bf16> {
-  static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
-    const uint2 r = *reinterpret_cast<const uint2*>(p);
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
-    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
-  }
-  static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
-    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-    uint2 w;
-    w.x = *reinterpret_cast<const uint32_t*>(&a);
-    w.y = *reinterpret_cast<const uint32_t*>(&b);
-    *reinterpret_cast<uint2*>(p) = w;
-  }
-};
-
-// A group of `lanes` lanes (a power of two, dim / 8 rounded up) serves one (token, head); a warp
-// serves 32 / lanes of them at once and two rounds per thread, with the loads of both rounds issued
-// before any arithmetic, so that enough bytes are in flight to keep the memory system busy.
+// A group of `lanes` lanes (a power of two) serves one (token, head), each lane one 16-byte piece of
+// each half of the head; a warp serves 32 / lanes heads at once and two rounds per thread, with the
+// loads of both rounds issued before any arithmetic, so that enough bytes are in flight.
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, const float* __restrict__ q_norm_w,
@@ -242,30 +221,36 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
                                        float eps, int lanes) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int ROUNDS = 2;
+  constexpr int ROUNDS = 2, N = Pack<T>::N;
   const int heads = q_heads + 2 * kv_heads, half = dim >> 1;
   const int per_warp = 32 / lanes;
-  const int lane = threadIdx.x & 31, sub = lane / lanes, i0 = (lane % lanes) * 4;
+  const int lane = threadIdx.x & 31, sub = lane / lanes, i0 = (lane % lanes) * N;
   const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long total = (long)tokens * heads;
   const bool mine = i0 < half;
 
   long item[ROUNDS];
-  float lo[ROUNDS][4], hi[ROUNDS][4], cs[ROUNDS][4], sn[ROUNDS][4];
-  const bool rotate = rope_table && i0 + 4 <= n_freq;    // n_freq = half whenever a table is given
+  float lo[ROUNDS][N], hi[ROUNDS][N], cs[ROUNDS][N], sn[ROUNDS][N];
+  const bool rotate = rope_table && i0 + N <= n_freq;    // n_freq = half whenever a table is given
 #pragma unroll
   for (int r = 0; r < ROUNDS; ++r) {
     item[r] = (warp * ROUNDS + r) * per_warp + sub;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { lo[r][j] = hi[r][j] = 0.f; cs[r][j] = 1.f; sn[r][j] = 0.f; }
+    for (int j = 0; j < N; ++j) { lo[r][j] = hi[r][j] = 0.f; cs[r][j] = 1.f; sn[r][j] = 0.f; }
     if (item[r] < total && mine) {
       const T* src = qkv + (size_t)item[r] * dim;
-      Quad<T>::load(src + i0, lo[r]);
-      Quad<T>::load(src + i0 + half, hi[r]);
+      Pack<T>::load(src + i0, lo[r]);
+      Pack<T>::load(src + i0 + half, hi[r]);
       if (rotate) {     // the table's values travel with the data, not after the reduction
         const float* cos_row = rope_table + ((size_t)(item[r] / heads) * 2) * n_freq + i0;
-        Pack<float>::load(cos_row, cs[r]);
-        Pack<float>::load(cos_row + n_freq, sn[r]);
+#pragma unroll
+        for (int j = 0; j < N; j += 4) {
+          float c4[4], s4[4];
+          Pack<float>::load(cos_row + j, c4);
+          Pack<float>::load(cos_row + n_freq + j, s4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { cs[r][j + e] = c4[e]; sn[r][j + e] = s4[e]; }
+        }
       }
     }
   }
@@ -293,7 +278,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
     const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) ss += lo[r][j] * lo[r][j] + hi[r][j] * hi[r][j];
+    for (int j = 0; j < N; ++j) ss += lo[r][j] * lo[r][j] + hi[r][j] * hi[r][j];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
       if (o < lanes) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -301,26 +286,24 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
     if (w) {
       const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < N; ++j) {
         lo[r][j] = Elem<T>::round(w[i0 + j] * Elem<T>::round(lo[r][j] * inv));
         hi[r][j] = Elem<T>::round(w[i0 + j + half] * Elem<T>::round(hi[r][j] * inv));
       }
     }
     if (rotate && (is_q || is_k)) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        {
-          const float c = Elem<T>::round(cs[r][j]), s = Elem<T>::round(sn[r][j]);
-          // rotate_half(x) = (-hi, lo): each product and the sum round to T
-          const float a = Elem<T>::round(Elem<T>::round(lo[r][j] * c) + Elem<T>::round(-hi[r][j] * s));
-          const float b = Elem<T>::round(Elem<T>::round(hi[r][j] * c) + Elem<T>::round(lo[r][j] * s));
-          lo[r][j] = a;
-          hi[r][j] = b;
-        }
+      for (int j = 0; j < N; ++j) {
+        const float c = Elem<T>::round(cs[r][j]), s = Elem<T>::round(sn[r][j]);
+        // rotate_half(x) = (-hi, lo): each product and the sum round to T
+        const float a = Elem<T>::round(Elem<T>::round(lo[r][j] * c) + Elem<T>::round(-hi[r][j] * s));
+        const float b = Elem<T>::round(Elem<T>::round(hi[r][j] * c) + Elem<T>::round(lo[r][j] * s));
+        lo[r][j] = a;
+        hi[r][j] = b;
       }
     }
-    Quad<T>::store(dst + i0, lo[r]);
-    Quad<T>::store(dst + i0 + half, hi[r]);
+    Pack<T>::store(dst + i0, lo[r]);
+    Pack<T>::store(dst + i0 + half, hi[r]);
   }
 }
 
@@ -329,11 +312,12 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
                                  const int* slot_map, int tokens, int q_heads, int kv_heads, int dim, int n_freq,
                                  int page_tokens, float eps, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (dim % 8 || dim > 256 || 2 * n_freq > dim) return LB_ERR_SIZE;   // four elements of each half per lane
+  if (dim % 16 || dim > 512 || 2 * n_freq > dim) return LB_ERR_SIZE;   // one 16-byte piece of each half per lane
   // a rotation pairs i with i + dim/2 only when the rotary part spans the whole head
   if (rope_table && 2 * n_freq != dim) return LB_ERR_SIZE;
+  const int piece = dtype == LB_BF16 ? 8 : 4;               // elements in 16 bytes
   int lanes = 1;
-  while (lanes * 8 < dim) lanes *= 2;                       // four elements of each half per lane
+  while (lanes * piece * 2 < dim) lanes *= 2;
   const long items = (long)tokens * (q_heads + 2 * kv_heads);
   const long warps = (items + 2 * (32 / lanes) - 1) / (2 * (32 / lanes));
   const int threads = 128;

@@ -37,7 +37,8 @@ def test_embed(dtype, vocab, hidden, tokens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows, hidden, eps", [(5, 96, 1e-5), (3, 2560, 1e-6), (2, 5000, 1e-6), (17, 16, 1e-3)])
+@pytest.mark.parametrize("rows, hidden, eps", [(5, 96, 1e-5), (3, 2560, 1e-6), (2, 5000, 1e-6), (17, 16, 1e-3),
+                                               (300, 2560, 1e-6), (257, 104, 1e-5)])
 def test_add_rmsnorm(dtype, rows, hidden, eps):
     x = torch.randn(rows, hidden, device="cuda").to(dtype)
     delta = (0.5 * torch.randn(rows, hidden, device="cuda")).to(dtype)
