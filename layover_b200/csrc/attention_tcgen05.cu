@@ -66,6 +66,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {   // one look, never suspends
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -179,6 +188,64 @@ struct Args {
   unsigned* counters;
 };
 
+// The producer warp's loop. K and V tiles are requested independently, each as soon as its own
+// stage is free: taken in turn, the K tile of a later step would queue behind a V stage that the
+// second product frees late. A tile is 128 / page_tokens pages x 2 halves of the head = up to 32
+// TMA copies; one thread issuing them one after the other spends over a hundred cycles on each,
+// more than the tile's arithmetic takes, so every lane issues one copy of the tile in the same
+// instruction. Lane 0 watches the barriers. `code` marks the kernel in the error word if the wait
+// runs out.
+template <int STAGES>
+__device__ __forceinline__ void produce_kv(const CUtensorMap* kv_map, const Args& args, uint8_t* k_s, uint8_t* v_s,
+                                           uint64_t* k_full, uint64_t* k_empty, uint64_t* v_full, uint64_t* v_empty,
+                                           const int* page_cache, const int* table, int tile_begin, int n_tiles,
+                                           int kv_head, volatile uint32_t* flag, int code, int lane) {
+  const int pages_per_tile = KEYS / args.page_tokens;
+  const int pg = lane >> 1, half = lane & 1;             // this lane's copy within a tile
+  const bool mine = pg < pages_per_tile;
+  int next_k = 0, next_v = 0;
+  uint32_t idle = 0;
+  while (next_k < n_tiles || next_v < n_tiles) {
+    bool moved = false;
+#pragma unroll
+    for (int kind = 0; kind < 2; ++kind) {
+      const int i = kind ? next_v : next_k;
+      if (i >= n_tiles) continue;
+      const int stage = i % STAGES;
+      uint64_t* empty = kind ? &v_empty[stage] : &k_empty[stage];
+      uint64_t* full = kind ? &v_full[stage] : &k_full[stage];
+      int ready = 0;
+      if (lane == 0) {
+        ready = mbar_test(empty, ((i / STAGES) & 1) ^ 1) ? 1 : 0;
+        if (ready) mbar_expect_tx(full, TILE_BYTES);
+      }
+      ready = __shfl_sync(0xffffffffu, ready, 0);
+      if (!ready) continue;
+      if (mine) {
+        uint8_t* dst = (kind ? v_s : k_s) + stage * TILE_BYTES;
+        const int page = page_at(page_cache, table, args.table_width, tile_begin * pages_per_tile,
+                                 (tile_begin + i) * pages_per_tile + pg);
+        tma_load_5d(dst + half * HALF_BYTES + pg * args.page_tokens * 128, kv_map, full, half * 64, 0, kv_head, page,
+                    args.layer2 + kind);
+      }
+      if (kind) ++next_v; else ++next_k;
+      moved = true;
+    }
+    int stop = 0;
+    if (lane == 0) {
+      if (moved) {
+        idle = 0;
+      } else if (++idle > SPIN_LIMIT) {
+        atomicCAS(&g_attn_error, 0, code); flag[0] = 1;
+      } else if (idle > 4096) {
+        __nanosleep(64);
+      }
+      stop = flag[0] ? 1 : 0;
+    }
+    if (__shfl_sync(0xffffffffu, stop, 0)) break;
+  }
+}
+
 constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * KV_STAGES) + 1024 + 512 + TABLE_CACHE * 4;   // Q, P, K and V stages, slack, barriers, table
 
 template <bool DECODE>
@@ -263,28 +330,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   if (warp == 0) {
     const int pages_per_tile = KEYS / args.page_tokens;
     if (n_tiles_mine > 0) cache_pages(page_cache, table, args.table_width, tile_begin * pages_per_tile, n_tiles_mine * pages_per_tile, lane);
-    if (lane == 0 && n_tiles_mine > 0) {
+    if (n_tiles_mine > 0) {
       // ---------------- producer: the query tile, then K and V page by page
-      mbar_expect_tx(q_full, TILE_BYTES);
-      for (int half = 0; half < 2; ++half)
-        tma_load_2d(q_s + half * HALF_BYTES, &q_map, q_full, (DECODE ? 0 : head * DIM) + half * 64, q_row);
-      for (int i = 0; i < n_tiles_mine && !flag[0]; ++i) {
-        const int tile = tile_begin + i, stage = i % KV_STAGES;
-        const uint32_t phase = (i / KV_STAGES) & 1;
-        for (int kind = 0; kind < 2; ++kind) {       // K first: the first product needs it first
-          uint64_t* empty = kind ? &v_empty[stage] : &k_empty[stage];
-          uint64_t* full = kind ? &v_full[stage] : &k_full[stage];
-          uint8_t* dst = (kind ? v_s : k_s) + stage * TILE_BYTES;
-          if (!mbar_wait(empty, phase ^ 1)) { atomicCAS(&g_attn_error, 0, 1); flag[0] = 1; break; }
-          mbar_expect_tx(full, TILE_BYTES);
-          for (int pg = 0; pg < pages_per_tile; ++pg) {
-            const int page = page_at(page_cache, table, args.table_width, tile_begin * pages_per_tile, tile * pages_per_tile + pg);
-            for (int half = 0; half < 2; ++half)
-              tma_load_5d(dst + half * HALF_BYTES + pg * args.page_tokens * 128, &kv_map, full, half * 64, 0, kv_head, page,
-                          args.layer2 + kind);
-          }
-        }
+      if (lane == 0) {
+        mbar_expect_tx(q_full, TILE_BYTES);
+        for (int half = 0; half < 2; ++half)
+          tma_load_2d(q_s + half * HALF_BYTES, &q_map, q_full, (DECODE ? 0 : head * DIM) + half * 64, q_row);
       }
+      produce_kv<KV_STAGES>(&kv_map, args, k_s, v_s, k_full, k_empty, v_full, v_empty, page_cache, table, tile_begin,
+                            n_tiles_mine, kv_head, flag, 1, lane);
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles_mine > 0) {
@@ -608,26 +662,13 @@ attention_tcgen05_decode_t_kernel(const __grid_constant__ CUtensorMap q_map, con
   if (warp == 0) {
     const int pages_per_tile = KEYS / args.page_tokens;
     if (n_mine > 0) cache_pages(page_cache, table, args.table_width, tile_begin * pages_per_tile, n_mine * pages_per_tile, lane);
-    if (lane == 0 && n_mine > 0) {
-      mbar_expect_tx(q_full, 2 * QT_HALF);
-      for (int half = 0; half < 2; ++half) tma_load_2d(q_s + half * QT_HALF, &q_map, q_full, half * 64, q_row);
-      for (int i = 0; i < n_mine && !flag[0]; ++i) {
-        const int tile = tile_begin + i, stage = i % T_STAGES;
-        const uint32_t phase = (i / T_STAGES) & 1;
-        for (int kind = 0; kind < 2; ++kind) {
-          uint64_t* empty = kind ? &v_empty[stage] : &k_empty[stage];
-          uint64_t* full = kind ? &v_full[stage] : &k_full[stage];
-          uint8_t* dst = (kind ? v_s : k_s) + stage * TILE_BYTES;
-          if (!mbar_wait(empty, phase ^ 1)) { atomicCAS(&g_attn_error, 0, 11); flag[0] = 1; break; }
-          mbar_expect_tx(full, TILE_BYTES);
-          for (int pg = 0; pg < pages_per_tile; ++pg) {
-            const int page = page_at(page_cache, table, args.table_width, tile_begin * pages_per_tile, tile * pages_per_tile + pg);
-            for (int half = 0; half < 2; ++half)
-              tma_load_5d(dst + half * HALF_BYTES + pg * args.page_tokens * 128, &kv_map, full, half * 64, 0, kv_head, page,
-                          args.layer2 + kind);
-          }
-        }
+    if (n_mine > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(q_full, 2 * QT_HALF);
+        for (int half = 0; half < 2; ++half) tma_load_2d(q_s + half * QT_HALF, &q_map, q_full, half * 64, q_row);
       }
+      produce_kv<T_STAGES>(&kv_map, args, k_s, v_s, k_full, k_empty, v_full, v_empty, page_cache, table, tile_begin, n_mine,
+                           kv_head, flag, 11, lane);
     }
   } else if (warp == 1) {
     if (lane == 0 && n_mine > 0) {
