@@ -37,7 +37,7 @@ constexpr int HALF_BYTES = ROWS * 128;          // one 64-column half of a 128-r
 constexpr int TILE_BYTES = 2 * HALF_BYTES;      // 32 KiB
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
 constexpr float RESCALE_THRESHOLD = 8.0f;       // in log2 units
 
 __device__ int g_attn_error = 0;   // 0 = ok; which wait ran out otherwise
@@ -128,6 +128,26 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) 
         "r"(__float_as_uint(v[15]))
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// 64 columns of this thread's lane, no wait: tmem_wait_ld() must come before the values are used.
+__device__ __forceinline__ void tmem_ld64_nowait(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (bf16, two elements of K per 32-bit column) is read from tensor memory
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -237,8 +257,8 @@ __device__ __forceinline__ void produce_kv(const CUtensorMap* kv_map, const Args
         idle = 0;
       } else if (++idle > SPIN_LIMIT) {
         atomicCAS(&g_attn_error, 0, code); flag[0] = 1;
-      } else if (idle > 4096) {
-        __nanosleep(64);
+      } else {
+        __nanosleep(idle > 4096 ? 256 : 20);    // leave the issue slots to the softmax warps of this scheduler
       }
       stop = flag[0] ? 1 : 0;
     }
@@ -584,6 +604,279 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   }
 }
 
+// ------------------------------------------------------------------------------- prompt portions, two heads per block
+// The kernel for prompt portions where an even number of query heads shares a KV head. A block
+// takes the same 128 tokens of TWO such heads: each head has its own query tile, score and output
+// accumulators in tensor memory and its own softmax warpgroup, and both read the same K and V
+// tiles. The MMA thread alternates between the heads (O_a += P_a V, S_a = Q_a K^T of the next
+// tile, then the same for b), so that the tensor cores work for one head while the other's
+// softmax runs. The probabilities never touch shared memory: each thread overwrites the scores of
+// its own row in tensor memory with them (bf16, two per column) and the second product reads its
+// A operand from there; products issued by one thread run in order, so the next tile's scores
+// land on those columns only after the product that read them.
+constexpr int PAIR_THREADS = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2-5 and 6-9 the softmax warpgroups
+constexpr int PAIR_SMEM = TILE_BYTES * (2 + 2 * KV_STAGES) + 1024 + 512 + TABLE_CACHE * 4;   // Q x2, K and V stages, slack, barriers, table
+
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                              const Args args) {
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;                                   // [2][TILE_BYTES]
+  uint8_t* k_s = q_s + 2 * TILE_BYTES;                   // [KV_STAGES][TILE_BYTES]
+  uint8_t* v_s = k_s + KV_STAGES * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2]
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [2 heads] the scores of a tile are in tensor memory
+  uint64_t* p_full = bars + 11;       // [2 heads] the probabilities are, and the output is rescaled
+  uint64_t* pv_done = bars + 13;      // [2 heads] the second product of a tile is finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile uint32_t* flag = tmem_slot + 1;   // [0] a wait ran out
+  int* page_cache = reinterpret_cast<int*>(bars) + 128;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = args.q_heads / args.kv_heads;
+  // heads run fastest and the tile list is walked backwards: later tiles of a sequence visit more keys
+  const int tile_index = gridDim.y - 1 - blockIdx.y;
+  const int seq = args.tile_seq[tile_index], q0 = args.tile_q0[tile_index];
+  const int head0 = 2 * blockIdx.x, kv_head = head0 / group;
+  const int row0 = args.cu_q[seq], q_len = args.cu_q[seq + 1] - row0, ctx = args.ctx_len[seq];
+  const int n_rows = min(ROWS, q_len - q0);
+  const int p_first = ctx - q_len + q0, p_last = p_first + n_rows - 1;
+  const int key_lo = args.window > 0 ? max(0, p_first - args.window + 1) : 0;
+  const int tile_begin = key_lo / KEYS, tile_end = p_last / KEYS + 1;
+  const int q_row = row0 + q0;
+  const int n_tiles = max(0, tile_end - tile_begin);
+  const int* table = args.block_table + (size_t)seq * args.table_width;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1);
+    }
+    flag[0] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;            // scores of head a, head b: 128 columns each
+  const uint32_t tmem_o = tmem_base + 256;      // outputs of head a, head b
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    const int pages_per_tile = KEYS / args.page_tokens;
+    if (n_tiles > 0) {
+      cache_pages(page_cache, table, args.table_width, tile_begin * pages_per_tile, n_tiles * pages_per_tile, lane);
+      if (lane == 0) {
+        mbar_expect_tx(q_full, 2 * TILE_BYTES);
+        for (int u = 0; u < 2; ++u)
+          for (int half = 0; half < 2; ++half)
+            tma_load_2d(q_s + u * TILE_BYTES + half * HALF_BYTES, &q_map, q_full, (head0 + u) * DIM + half * 64, q_row);
+      }
+      produce_kv<KV_STAGES>(&kv_map, args, k_s, v_s, k_full, k_empty, v_full, v_empty, page_cache, table, tile_begin,
+                            n_tiles, kv_head, flag, 21, lane);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = instr_desc(false), idesc_o = instr_desc(true);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) { atomicCAS(&g_attn_error, 0, 22); flag[0] = 1; }
+      auto issue_s = [&](int i, int u) {          // S_u = Q_u K(i)^T; K(i) has been waited for
+        const int stage = i % KV_STAGES;
+        const uint32_t q_addr = smem_u32(q_s + u * TILE_BYTES), k_addr = smem_u32(k_s + stage * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < DIM / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_bf16(tmem_s + u * 128, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[u]);
+        if (u == 1) umma_commit(&k_empty[stage]);
+      };
+      if (ok) {
+        ok = mbar_wait(&k_full[0], 0);
+        if (!ok) { atomicCAS(&g_attn_error, 0, 23); flag[0] = 1; }
+      }
+      if (ok) {
+        fence_after_sync();
+        issue_s(0, 0);
+        issue_s(0, 1);
+      }
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int stage = i % KV_STAGES;
+        for (int u = 0; u < 2 && ok; ++u) {
+          if (!mbar_wait(&p_full[u], i & 1) || (u == 0 && !mbar_wait(&v_full[stage], (i / KV_STAGES) & 1))) {
+            atomicCAS(&g_attn_error, 0, 24); flag[0] = 1; ok = false; break;
+          }
+          fence_after_sync();
+          const uint32_t v_addr = smem_u32(v_s + stage * TILE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < KEYS / 16; ++ks)       // 16 keys: 8 columns of packed probabilities, 16 rows of V
+            umma_bf16_ts(tmem_o + u * 128, tmem_s + u * 128 + ks * 8, desc_mn_major(v_addr + ks * 16 * 128), idesc_o,
+                         (i > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&pv_done[u]);
+          if (u == 1) umma_commit(&v_empty[stage]);
+          if (i + 1 < n_tiles) {
+            if (u == 0 && !mbar_wait(&k_full[(i + 1) % KV_STAGES], ((i + 1) / KV_STAGES) & 1)) {
+              atomicCAS(&g_attn_error, 0, 25); flag[0] = 1; ok = false; break;
+            }
+            fence_after_sync();
+            issue_s(i + 1, u);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax and epilogue: warpgroup u owns head u, one query row per thread
+    const int u = (warp - 2) >> 2;
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t my_s = tmem_s + u * 128 + lane_addr, my_o = tmem_o + u * 128 + lane_addr;
+    const int p_row = p_first + row;                          // rows past n_rows are ballast
+    const float c = args.scale_log2;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int tile = tile_begin + i, stage = i % KV_STAGES;
+      const int key0 = tile * KEYS;
+      if (!mbar_wait(&s_full[u], i & 1)) { atomicCAS(&g_attn_error, 0, 26); flag[0] = 1; ok = false; break; }
+      fence_after_sync();
+      const bool masked = key0 + KEYS - 1 > p_first || key0 < key_lo || args.window > 0;
+      float s[KEYS];
+      {
+        uint32_t raw[64];
+        tmem_ld64_nowait(my_s, raw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 64; ++e) s[e] = __uint_as_float(raw[e]);
+        tmem_ld64_nowait(my_s + 64, raw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 64; ++e) s[64 + e] = __uint_as_float(raw[e]);
+      }
+      if (masked) {
+#pragma unroll
+        for (int e = 0; e < KEYS; ++e) {
+          const int key = key0 + e;
+          const bool seen = key <= p_row && key >= key_lo && (args.window <= 0 || p_row - key < args.window);
+          if (!seen) s[e] = -INFINITY;
+        }
+      }
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < KEYS; ++e) tile_max = fmaxf(tile_max, s[e]);
+      // the reference maximum only moves when the true one has outgrown it by 2^8 (see the kernel above)
+      const bool grow = (tile_max - m_ref) * c > RESCALE_THRESHOLD || (m_ref == -INFINITY && tile_max > -INFINITY);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
+      const float m_new = grow ? tile_max : m_ref;
+      const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * c);
+      const float neg_base = (m_new == -INFINITY) ? 0.f : -m_new * c;
+      float tile_sum = 0.f;
+      // exponentials, 32 scores at a time: 16 columns of packed probabilities over the row's own scores
+#pragma unroll
+      for (int ch = 0; ch < KEYS / 32; ++ch) {
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float a = fast_exp2(fmaf(s[ch * 32 + 2 * e], c, neg_base));
+          const float b = fast_exp2(fmaf(s[ch * 32 + 2 * e + 1], c, neg_base));
+          tile_sum += a + b;
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+          w[e] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        tmem_st16_nowait(my_s + ch * 16, w);
+      }
+      l_sum = l_sum * factor + tile_sum;
+      m_ref = m_new;
+      if (any_grow && i > 0) {
+        // the previous product of this head must be finished before its accumulator is touched
+        if (!mbar_wait(&pv_done[u], (i - 1) & 1)) { atomicCAS(&g_attn_error, 0, 27); flag[0] = 1; ok = false; break; }
+        fence_after_sync();
+#pragma unroll
+        for (int ch = 0; ch < DIM / 16; ++ch) {
+          float v[16];
+          tmem_ld16(my_o + ch * 16, v);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] *= factor;
+          tmem_st16(my_o + ch * 16, v);
+        }
+      }
+      // V rows of keys outside the context may hold anything: zero them (0 x NaN would be NaN).
+      // Both warpgroups do it, each before its own product is released.
+      const int limit = p_last + 1;
+      if (key0 + KEYS > limit || key0 < key_lo) {
+        if (!mbar_wait(&v_full[stage], (i / KV_STAGES) & 1)) { atomicCAS(&g_attn_error, 0, 28); flag[0] = 1; ok = false; break; }
+        const int key = key0 + row;
+        if (key >= limit || key < key_lo) {
+          uint8_t* vrow = v_s + stage * TILE_BYTES + row * 128;
+#pragma unroll
+          for (int chunk = 0; chunk < 8; ++chunk) {
+            *reinterpret_cast<uint4*>(vrow + chunk * 16) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vrow + HALF_BYTES + chunk * 16) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        fence_async_smem();
+      }
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[u]);
+    }
+
+    // ---- the head's result: wait for its last product, read the row, divide, store
+    if (ok && n_tiles > 0) {
+      if (!mbar_wait(&pv_done[u], (n_tiles - 1) & 1)) { atomicCAS(&g_attn_error, 0, 29); flag[0] = 1; ok = false; }
+      fence_after_sync();
+    }
+    if (ok) {
+      // tensor-memory loads are warp-wide: every lane reads its row, rows of the tile only are stored
+      const bool valid = row < n_rows;
+      bf16* dst = args.out + ((size_t)(q_row + (valid ? row : 0)) * args.q_heads + head0 + u) * DIM;
+      const float inv = 1.0f / l_sum;
+#pragma unroll
+      for (int ch = 0; ch < DIM / 16; ++ch) {
+        float v[16];
+        if (n_tiles > 0) {
+          tmem_ld16(my_o + ch * 16, v);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = 0.f;
+        }
+        if (!valid) continue;
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * e] * inv, v[2 * e + 1] * inv);
+          w[e] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        reinterpret_cast<uint4*>(dst + ch * 16)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(dst + ch * 16)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    }
+  }
+
+  // ---------------- teardown
+  fence_before_sync();
+  __syncthreads();
+  if (flag[0]) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies in flight land
+    __syncthreads();
+  }
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------------------- decode, keys on the rows
 // The decode kernel proper. With one new token per sequence there are only `group` query rows, so
 // the products are turned around: S^T = K Q^T puts the 128 keys of a tile on the rows of the MMA
@@ -912,6 +1205,7 @@ void configure_once() {
   cudaFuncSetAttribute(attention_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   cudaFuncSetAttribute(attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   cudaFuncSetAttribute(attention_tcgen05_decode_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+  cudaFuncSetAttribute(attention_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
   done = true;
 }
 
@@ -978,8 +1272,13 @@ LB_EXPORT int lb_attention_tcgen05_prefill(const void* q, long q_rows, const voi
   memcpy(&kv_map, pool_map, sizeof(kv_map));
   Args args{(bf16*)out, block_table, table_width, cu_q, ctx_len, tile_seq, tile_q0, q_heads, kv_heads, page_tokens, window,
             2 * layer, scale * 1.4426950408889634f, 1, nullptr, nullptr};
-  const int code = lb_launch(attention_tcgen05_kernel<false>, dim3(q_heads, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES,
-                             stream, q_map, kv_map, args);
+  int code;
+  if ((q_heads / kv_heads) % 2 == 0)    // two heads of a KV head per block
+    code = lb_launch(attention_tcgen05_pair_kernel, dim3(q_heads / 2, n_tiles), dim3(PAIR_THREADS), (size_t)PAIR_SMEM, stream,
+                     q_map, kv_map, args);
+  else
+    code = lb_launch(attention_tcgen05_kernel<false>, dim3(q_heads, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES, stream,
+                     q_map, kv_map, args);
   return code ? code : lb_last_error();
 }
 

@@ -493,9 +493,11 @@ def test_attention_tcgen05_decode(q_heads, kv_heads, page, splits):
         close(got, expected, torch.bfloat16)
 
 
-def test_attention_tcgen05_scores_far_apart_force_rescaling():
+@pytest.mark.parametrize("heads", [1, 2])
+def test_attention_tcgen05_scores_far_apart_force_rescaling(heads):
     """Keys whose scores grow along the sequence make the running maximum jump by far more than the
-    2^8 that the kernel tolerates before it rescales its accumulated output."""
+    2^8 that the kernel tolerates before it rescales its accumulated output. One head goes through
+    the kernel with a head per block, two through the one with two heads per block."""
     o = ops()
     dim, n, page = 128, 640, 16
     gen = torch.Generator().manual_seed(9)
@@ -506,15 +508,16 @@ def test_attention_tcgen05_scores_far_apart_force_rescaling():
         k = (direction * (key / 8.0) * math.sqrt(dim) / 10.0).to(torch.bfloat16)
         k_pool[int(table[0, key // page]), 0, key % page] = k.cuda()
         ks[0][key, 0] = k
-    q = (direction * 10.0).to(torch.bfloat16).view(1, 1, dim).repeat(n, 1, 1)
+    q = (direction * 10.0).to(torch.bfloat16).view(1, 1, dim).repeat(n, heads, 1)
+    q[:, -1] *= 0.5                                            # the heads differ
     pool = torch.stack((k_pool, v_pool))[None].contiguous()
-    qf = q.reshape(n, dim).cuda()
+    qf = q.reshape(n, heads * dim).cuda()
     out = torch.empty_like(qf)
     cu = torch.tensor([0, n], dtype=torch.int32, device="cuda")
     ctx = torch.tensor([n], dtype=torch.int32, device="cuda")
     tiles = list(range(0, n, 128))
     o.attention_tcgen05_prefill(qf, pool, 0, out, table, cu, ctx, torch.zeros(len(tiles), dtype=torch.int32, device="cuda"),
-                                torch.tensor(tiles, dtype=torch.int32, device="cuda"), len(tiles), 1, 1, dim, page, 1 / math.sqrt(dim))
+                                torch.tensor(tiles, dtype=torch.int32, device="cuda"), len(tiles), heads, 1, dim, page, 1 / math.sqrt(dim))
     assert o.attention_tcgen05_status() == 0
     expected = plain_attention(q, ks[0], vs[0])
-    close(out.cpu().view(n, 1, dim), expected, torch.bfloat16)
+    close(out.cpu().view(n, heads, dim), expected, torch.bfloat16)
