@@ -198,7 +198,7 @@ LB_EXPORT int lb_rope_table(const int* positions, const float* inv_freq, float* 
 }
 
 // ---------------------------------------------------------------- QK-norm + rotary + KV write
-// One warp per (token, head) of the fused projection row [q heads | k heads | v heads] x dim
+// Over the (token, head) items of the fused projection row [q heads | k heads | v heads] x dim
 // (dim a multiple of 16; rows, outputs and pages 16-byte aligned).
 //   q, k: per-head RMSNorm over dim (weight shared by the heads, layover/model.py:124-125), then
 //         x*cos + rotate_half(x)*sin with cos/sin from the step's table, rounded to T
@@ -209,10 +209,11 @@ LB_EXPORT int lb_rope_table(const int* positions, const float* inv_freq, float* 
 // Null norm weights skip the norm, a null table skips the rotation, null pools skip the write
 // (then k is written back in place into the projection row, for a position encoding that runs
 // as a separate step), a null q_out skips the q heads (the pass that only writes pages).
-// A group of `lanes` lanes (a power of two) serves one (token, head), each lane one 16-byte piece of
-// each half of the head; a warp serves 32 / lanes heads at once and two rounds per thread, with the
-// loads of both rounds issued before any arithmetic, so that enough bytes are in flight.
-template <typename T>
+// A group of `lanes` lanes (a power of two) serves ROUNDS consecutive heads of ONE token (ROUNDS
+// divides the number of heads), each lane one 16-byte piece of each half of a head; a warp serves
+// 32 / lanes such groups. The token's cos/sin pieces are read once for all the group's heads, and
+// the loads of all rounds are issued before any arithmetic, so that enough bytes are in flight.
+template <typename T, int ROUNDS>
 __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, const float* __restrict__ q_norm_w,
                                        const float* __restrict__ k_norm_w, const float* __restrict__ rope_table,
@@ -221,43 +222,46 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
                                        float eps, int lanes) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int ROUNDS = 2, N = Pack<T>::N;
+  constexpr int N = Pack<T>::N;
   const int heads = q_heads + 2 * kv_heads, half = dim >> 1;
   const int per_warp = 32 / lanes;
   const int lane = threadIdx.x & 31, sub = lane / lanes, i0 = (lane % lanes) * N;
   const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long total = (long)tokens * heads;
-  const bool mine = i0 < half;
+  const long first = (warp * per_warp + sub) * ROUNDS;      // this group's heads: first .. first + ROUNDS - 1
+  const bool mine = i0 < half, live = first < total;        // heads % ROUNDS == 0: a group is all live or all not
+  const int t = live ? (int)(first / heads) : 0, h0 = live ? (int)(first % heads) : 0;
 
-  long item[ROUNDS];
-  float lo[ROUNDS][N], hi[ROUNDS][N], cs[ROUNDS][N], sn[ROUNDS][N];
+  float lo[ROUNDS][N], hi[ROUNDS][N], cs[N], sn[N];
   const bool rotate = rope_table && i0 + N <= n_freq;    // n_freq = half whenever a table is given
 #pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
-    item[r] = (warp * ROUNDS + r) * per_warp + sub;
+  for (int j = 0; j < N; ++j) { cs[j] = 1.f; sn[j] = 0.f; }
 #pragma unroll
-    for (int j = 0; j < N; ++j) { lo[r][j] = hi[r][j] = 0.f; cs[r][j] = 1.f; sn[r][j] = 0.f; }
-    if (item[r] < total && mine) {
-      const T* src = qkv + (size_t)item[r] * dim;
+  for (int r = 0; r < ROUNDS; ++r) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) lo[r][j] = hi[r][j] = 0.f;
+    if (live && mine) {
+      const T* src = qkv + (size_t)(first + r) * dim;
       Pack<T>::load(src + i0, lo[r]);
       Pack<T>::load(src + i0 + half, hi[r]);
-      if (rotate) {     // the table's values travel with the data, not after the reduction
-        const float* cos_row = rope_table + ((size_t)(item[r] / heads) * 2) * n_freq + i0;
-#pragma unroll
-        for (int j = 0; j < N; j += 4) {
-          float c4[4], s4[4];
-          Pack<float>::load(cos_row + j, c4);
-          Pack<float>::load(cos_row + n_freq + j, s4);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) { cs[r][j + e] = c4[e]; sn[r][j + e] = s4[e]; }
-        }
-      }
     }
   }
+  if (live && mine && rotate && h0 < q_heads + kv_heads) {     // the table's values travel with the data
+    const float* cos_row = rope_table + ((size_t)t * 2) * n_freq + i0;
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      float c4[4], s4[4];
+      Pack<float>::load(cos_row + j, c4);
+      Pack<float>::load(cos_row + n_freq + j, s4);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { cs[j + e] = Elem<T>::round(c4[e]); sn[j + e] = Elem<T>::round(s4[e]); }
+    }
+  }
+  int slot = 0;
+  if (live && h0 + ROUNDS > q_heads && (k_pool || v_pool)) slot = slot_map[t];
 #pragma unroll
   for (int r = 0; r < ROUNDS; ++r) {
-    const bool live = item[r] < total;        // whole groups agree, but every lane joins the shuffles
-    const int t = live ? (int)(item[r] / heads) : 0, h = live ? (int)(item[r] % heads) : 0;
+    const int h = h0 + r;
     const bool is_q = h < q_heads, is_k = !is_q && h < q_heads + kv_heads;
     T* dst = nullptr;
     if (live) {
@@ -267,11 +271,10 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
         T* pool = is_k ? k_pool : v_pool;
         if (pool) {
           const int kvh = is_k ? h - q_heads : h - q_heads - kv_heads;
-          const int slot = slot_map[t];
           const size_t page = slot / page_tokens, within = slot % page_tokens;
           dst = pool + ((page * kv_heads + kvh) * page_tokens + within) * dim;
         } else {
-          dst = is_k ? qkv + (size_t)item[r] * dim : nullptr;              // k goes back in place, v stays
+          dst = is_k ? qkv + (size_t)(first + r) * dim : nullptr;          // k goes back in place, v stays
         }
       }
     }
@@ -281,7 +284,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
     for (int j = 0; j < N; ++j) ss += lo[r][j] * lo[r][j] + hi[r][j] * hi[r][j];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
-      if (o < lanes) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (o < lanes) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // whole groups agree, every lane joins
     if (!dst || !mine) continue;
     if (w) {
       const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
@@ -294,10 +297,9 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
     if (rotate && (is_q || is_k)) {
 #pragma unroll
       for (int j = 0; j < N; ++j) {
-        const float c = Elem<T>::round(cs[r][j]), s = Elem<T>::round(sn[r][j]);
         // rotate_half(x) = (-hi, lo): each product and the sum round to T
-        const float a = Elem<T>::round(Elem<T>::round(lo[r][j] * c) + Elem<T>::round(-hi[r][j] * s));
-        const float b = Elem<T>::round(Elem<T>::round(hi[r][j] * c) + Elem<T>::round(lo[r][j] * s));
+        const float a = Elem<T>::round(Elem<T>::round(lo[r][j] * cs[j]) + Elem<T>::round(-hi[r][j] * sn[j]));
+        const float b = Elem<T>::round(Elem<T>::round(hi[r][j] * cs[j]) + Elem<T>::round(lo[r][j] * sn[j]));
         lo[r][j] = a;
         hi[r][j] = b;
       }
@@ -305,6 +307,38 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
     Pack<T>::store(dst + i0, lo[r]);
     Pack<T>::store(dst + i0 + half, hi[r]);
   }
+}
+
+template <typename T, int ROUNDS>
+static void launch_qk_norm_rope_kv(void* qkv, void* q_out, void* k_pool, void* v_pool, const float* q_norm_w,
+                                   const float* k_norm_w, const float* rope_table, const int* slot_map, int tokens,
+                                   int q_heads, int kv_heads, int dim, int n_freq, int page_tokens, float eps, int lanes,
+                                   cudaStream_t stream) {
+  const long groups = (long)tokens * (q_heads + 2 * kv_heads) / ROUNDS;
+  const int per_warp = 32 / lanes, threads = 128;
+  const long warps = (groups + per_warp - 1) / per_warp;
+  const long blocks = (warps * 32 + threads - 1) / threads;
+  lb_launch(qk_norm_rope_kv_kernel<T, ROUNDS>, (unsigned)blocks, threads, 0, stream, (T*)qkv, (T*)q_out, (T*)k_pool,
+            (T*)v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads, kv_heads, dim, n_freq, page_tokens, eps,
+            lanes);
+}
+
+template <typename T>
+static void dispatch_qk_norm_rope_kv(void* qkv, void* q_out, void* k_pool, void* v_pool, const float* q_norm_w,
+                                     const float* k_norm_w, const float* rope_table, const int* slot_map, int tokens,
+                                     int q_heads, int kv_heads, int dim, int n_freq, int page_tokens, float eps, int lanes,
+                                     cudaStream_t stream) {
+  const int heads = q_heads + 2 * kv_heads;
+  // few tokens: one head per group keeps more blocks busy; many: four heads share the table's row
+  if (heads % 4 == 0 && tokens >= 64)
+    launch_qk_norm_rope_kv<T, 4>(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
+                                 kv_heads, dim, n_freq, page_tokens, eps, lanes, stream);
+  else if (heads % 2 == 0)
+    launch_qk_norm_rope_kv<T, 2>(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
+                                 kv_heads, dim, n_freq, page_tokens, eps, lanes, stream);
+  else
+    launch_qk_norm_rope_kv<T, 1>(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
+                                 kv_heads, dim, n_freq, page_tokens, eps, lanes, stream);
 }
 
 LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool, void* v_pool,
@@ -318,18 +352,12 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
   const int piece = dtype == LB_BF16 ? 8 : 4;               // elements in 16 bytes
   int lanes = 1;
   while (lanes * piece * 2 < dim) lanes *= 2;
-  const long items = (long)tokens * (q_heads + 2 * kv_heads);
-  const long warps = (items + 2 * (32 / lanes) - 1) / (2 * (32 / lanes));
-  const int threads = 128;
-  const long blocks = (warps * 32 + threads - 1) / threads;
   if (dtype == LB_F32)
-    lb_launch(qk_norm_rope_kv_kernel<float>, (unsigned)blocks, threads, 0, stream, 
-        (float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens,
-        q_heads, kv_heads, dim, n_freq, page_tokens, eps, lanes);
+    dispatch_qk_norm_rope_kv<float>(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
+                                    kv_heads, dim, n_freq, page_tokens, eps, lanes, stream);
   else if (dtype == LB_BF16)
-    lb_launch(qk_norm_rope_kv_kernel<bf16>, (unsigned)blocks, threads, 0, stream, 
-        (bf16*)qkv, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
-        kv_heads, dim, n_freq, page_tokens, eps, lanes);
+    dispatch_qk_norm_rope_kv<bf16>(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, rope_table, slot_map, tokens, q_heads,
+                                   kv_heads, dim, n_freq, page_tokens, eps, lanes, stream);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();
