@@ -24,8 +24,19 @@ TINY = {
               num_key_value_heads=1, head_dim=32, max_position_embeddings=512, rope_theta=1000000.0,
               rms_norm_eps=1e-5, tie_word_embeddings=False),
 }
-TINY_INIT = {"a": dict(std=0.02, norm_std=0.1), "b": dict(std=0.05, norm_std=0.2)}
-TINY_PAGE = {"a": 4, "b": 16}
+# Two more with the head size of the served models, the only one the tensor-core attention takes:
+# "c" has an even number of query heads per KV head (two heads per block), "d" an odd one.
+TINY.update({
+    "c": dict(vocab_size=384, hidden_size=256, intermediate_size=320, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=128, max_position_embeddings=512, rope_theta=1000000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=False),
+    "d": dict(vocab_size=320, hidden_size=192, intermediate_size=256, num_hidden_layers=2, num_attention_heads=3,
+              num_key_value_heads=1, head_dim=128, max_position_embeddings=512, rope_theta=10000.0,
+              rms_norm_eps=1e-5, tie_word_embeddings=True),
+})
+TINY_INIT = {"a": dict(std=0.02, norm_std=0.1), "b": dict(std=0.05, norm_std=0.2), "c": dict(std=0.04, norm_std=0.1),
+             "d": dict(std=0.05, norm_std=0.2)}
+TINY_PAGE = {"a": 4, "b": 16, "c": 16, "d": 8}
 
 
 def pytest_configure(config):
@@ -50,7 +61,7 @@ def tolerance(reference: torch.Tensor, dtype: torch.dtype) -> float:
 
 @pytest.fixture(scope="session")
 def tiny_folders(tmp_path_factory):
-    """name -> (folder, raw config dict, weights by name as stored) for the two tiny models."""
+    """name -> (folder, raw config dict, weights by name as stored) for the tiny models."""
     from safetensors.torch import load_file
 
     import layover_b200 as lb

@@ -18,7 +18,8 @@ from replay_helpers import max_live_tokens, mixed, portions, run_trace, tail_dec
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"a": [5, 17, 33, 70, 100, 41], "b": [1, 9, 64, 130, 77, 200]}
+LENGTHS = {"a": [5, 17, 33, 70, 100, 41], "b": [1, 9, 64, 130, 77, 200], "c": [5, 140, 33, 300, 129, 260],
+           "d": [1, 257, 64, 130, 77, 200]}
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
@@ -66,6 +67,19 @@ def test_every_cut_matches_the_plain_implementation(tiny_folders, tmp_path, name
         assert any(len(e["tokens"]) > 1 for s in steps for e in s["entries"] if len(s["entries"]) > 1)
     rows = run_trace(folder, dtype_name, steps, tmp_path, block_tokens=TINY_PAGE[name])
     compare(rows, expected_rows(tiny_folders, name, dtype_name), DTYPES[dtype_name])
+
+
+@pytest.mark.parametrize("name", ["c", "d"])
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_every_cut_at_the_served_head_size(tiny_folders, tmp_path, name, cut):
+    """Head size 128 in bfloat16: prompt portions go through the tensor-core attention, with portions
+    that start inside a tile of 128 keys and pages that are used again."""
+    folder, _, _ = tiny_folders[name]
+    requests = requests_for(name)
+    # portions longer than a tile of 128 queries too, starting anywhere
+    steps = portions(requests, sizes=(2, 150, 3, 131, 2, 33, 5, 1, 64, 2)) if cut == "portions" else CUTS[cut](requests)
+    rows = run_trace(folder, "bfloat16", steps, tmp_path, block_tokens=TINY_PAGE[name])
+    compare(rows, expected_rows(tiny_folders, name, "bfloat16"), torch.bfloat16)
 
 
 @pytest.mark.parametrize("name", ["a", "b"])
