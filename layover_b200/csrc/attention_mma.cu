@@ -391,8 +391,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   bf16* v_s = k_s + STAGES * BKEYS * stride;
   __shared__ unsigned last_flag;
   __shared__ int table_cache[TABLE_CACHE];
+  // Lengths and block tables are written when the step begins, and the keys of earlier positions by
+  // earlier steps: the block reads them, and requests its first tiles, while the kernel before it
+  // still runs. What that kernel writes, the query and the tile that holds the newest key, is
+  // fetched after the wait.
   pdl_launch_dependents();
-  pdl_wait();
 
   const int seq = seq_list ? seq_list[blockIdx.x] : blockIdx.x;
   const int kv_head = blockIdx.y, split = blockIdx.z;
@@ -413,6 +416,15 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
   __syncthreads();
 
+  const int newest_tile = p / BKEYS;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (tile_begin + s < tile_end && tile_begin + s != newest_tile)
+      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_begin + s, key_lo, ctx,
+                   shape);
+    cp_async_commit();
+  }
+  pdl_wait();
   {
     const int chunks = dim >> 3;
     for (int i = threadIdx.x; i < 16 * chunks; i += THREADS) {
@@ -424,11 +436,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   }
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (tile_begin + s < tile_end)
+    if (tile_begin + s < tile_end && tile_begin + s == newest_tile)
       load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_begin + s, key_lo, ctx,
                    shape);
-    cp_async_commit();
   }
+  cp_async_commit();     // the query and the held tile: one more group than the ring has stages
 
   uint32_t qf[KSTEPS][4];
   float o[NT_O][4];
@@ -448,7 +460,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                    ctx, shape);
     }
     cp_async_commit();
-    cp_async_wait<STAGES - 1>();
+    // the first tile also waits for the group of the query, which was committed after the ring's
+    if (i == 0) cp_async_wait<1>(); else cp_async_wait<STAGES - 1>();
     __syncthreads();
     if (i == 0) {
 #pragma unroll
