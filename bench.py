@@ -294,7 +294,26 @@ def kernel_points(args) -> dict:
         out["attention_decode"][f"b{batch}_ctx{ctx}"] = {
             "us": round(t * 1e3, 1), "splits": splits, "tb_s": round(batch * ctx * nkv * d * 4 / t / 1e9, 2)}
         del pools
-    return {"only": "kernels", **out, "gemm_status": ops.gemm_status()}
+    # one prompt of 2,048 tokens through the prompt-portion attention (tcgen05 where it takes the sizes)
+    tokens = PREFILL_TOKENS
+    if ops.attention_tcgen05_supports(nq, nkv, d, page):
+        n_pages = -(-tokens // page)
+        layers = 4
+        pools = torch.randn(layers, 2, n_pages + 1, nkv, page, d, device="cuda").to(torch.bfloat16)
+        table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(1, n_pages)
+        q = torch.randn(tokens, nq * d, device="cuda").to(torch.bfloat16)
+        o = torch.empty_like(q)
+        cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+        lens = torch.tensor([tokens], dtype=torch.int32, device="cuda")
+        n_tiles = -(-tokens // ops.TCGEN05_TILE)
+        tile_seq = torch.zeros(n_tiles, dtype=torch.int32, device="cuda")
+        tile_q0 = torch.arange(n_tiles, dtype=torch.int32, device="cuda") * ops.TCGEN05_TILE
+        t = graph_time(lambda i: ops.attention_tcgen05_prefill(q, pools, i % layers, o, table, cu, lens, tile_seq, tile_q0,
+                                                               n_tiles, nq, nkv, d, page, 1 / math.sqrt(d), 0), layers)
+        flops = 4.0 * nq * d * tokens * (tokens + ops.TCGEN05_TILE) / 2      # both products, causal tiles
+        out["attention_prefill"] = {f"t{tokens}": {"us": round(t * 1e3, 1), "tflops": round(flops / t / 1e9, 0)}}
+        del pools
+    return {"only": "kernels", **out, "gemm_status": ops.gemm_status(), "attention_status": ops.attention_tcgen05_status()}
 
 
 def run_ours(args) -> dict:
