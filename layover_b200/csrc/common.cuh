@@ -97,3 +97,24 @@ static inline int lb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   config.numAttrs = lb_pdl_enabled() ? 1 : 0;
   return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
+
+// The same with the blocks of one z column launched as a thread-block cluster of `cluster_z` blocks.
+template <typename... KArgs, typename... Args>
+static inline int lb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    unsigned cluster_z, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 1;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = cluster_z;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = lb_pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}

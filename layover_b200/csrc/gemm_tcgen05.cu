@@ -168,13 +168,39 @@ template <int BN> struct SmallTile {
   static constexpr int BLOCKS_PER_SM = 2;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int RECV_BYTES = BM * BN * 4;         // what a block of a cluster receives: its rows of every split
+  static constexpr int SMEM_CLUSTER = SMEM + RECV_BYTES;
 };
+
+// Thread-block clusters: the blocks that hold the K ranges of one tile are launched as one cluster
+// and hand their partial sums to one another through distributed shared memory.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {   // the same address in another block
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void store_remote4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {    // every thread of every block of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 // The few-token kernel: D[i, j] = sum_k W[i, k] X[j, k] with 128 weight rows i per block, C[j, i] = D.
 // One tile (or one K range of a tile) per block, two blocks per SM, four warps that all join the
 // epilogue: for these short streams it starts and ends a few microseconds sooner than the
 // persistent kernel below.
-template <int BN, typename OutT, int EPI>
+// CLUSTER: the `splits` blocks of a tile are one cluster (grid z = cluster z = splits, a power of
+// two). Block r owns rows r * 128 / splits .. of the tile: every block sends those rows of its
+// accumulator into r's shared memory, and after the cluster's barrier r adds them in split order
+// and stores them. No scratch memory, fence, counter or last block: the sum starts one barrier
+// after the slowest block's last MMA.
+template <int BN, typename OutT, int EPI, bool CLUSTER = false>
 __global__ void __launch_bounds__(SMALL_THREADS, SmallTile<BN>::BLOCKS_PER_SM)
 gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, int K, int splits,
@@ -258,9 +284,33 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int valid_cols = min(BN, rows_b - n0);
   const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-  float* my_partial = partials ? partials + ((size_t)tile_id * splits + split) * BN * BM : nullptr;
+  float* my_partial = (partials && !CLUSTER) ? partials + ((size_t)tile_id * splits + split) * BN * BM : nullptr;
 
-  if (ready) {
+  if (CLUSTER) {
+    const int rows_per = BM / splits;
+    float* recv = reinterpret_cast<float*>(smem + T::STAGES * T::STAGE_BYTES + 256);   // [splits][rows_per][BN]
+    const uint32_t owner = (uint32_t)(row / rows_per);
+    const uint32_t dst = map_to_rank(smem_u32(recv + ((size_t)split * rows_per + row % rows_per) * BN), owner);
+    for (int c = 0; c < BN; c += 16) {
+      float v[16];
+      if (ready) {
+        tmem_ld16(lane_base + c, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) store_remote4(dst + (c + i) * 4, v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+    cluster_barrier();           // reached by every thread, also after a wait that ran out
+    const int first_row = m0 + (int)cluster_rank() * rows_per;
+    for (int idx = threadIdx.x; idx < rows_per * valid_cols; idx += SMALL_THREADS) {
+      const int j = idx / rows_per, r = idx % rows_per;
+      float sum = 0.f;
+      for (int sp = 0; sp < splits; ++sp) sum += recv[((size_t)sp * rows_per + r) * BN + j];
+      if (first_row + r < rows_a) store_one<OutT>(C + (size_t)(n0 + j) * ldc + first_row + r, sum);
+    }
+  } else if (ready) {
     for (int c = 0; c < BN; c += 16) {
       if (c >= valid_cols) break;                           // uniform over the block
       float v[16];
@@ -306,7 +356,7 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
   }
 
-  if (splits > 1) {
+  if (!CLUSTER && splits > 1) {
     // the block that arrives last at this tile's counter adds the partial tiles in split order
     __threadfence();
     __syncthreads();
@@ -825,6 +875,15 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
   return code ? code : lb_last_error();
 }
 
+// LAYOVER_B200_CLUSTER_REDUCE=0 sends split products through scratch memory and a counter instead.
+static bool lb_cluster_reduce_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("LAYOVER_B200_CLUSTER_REDUCE");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
+
 template <int BN, typename OutT, int EPI = 0>
 int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb,
                     cudaStream_t stream) {
@@ -854,6 +913,20 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
     if (splits < 1) splits = 1;
   }
   dim3 grid(tiles, (pb.rows_b + BN - 1) / BN, splits);
+  if (EPI == 0 && BN <= 32 && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && lb_cluster_reduce_enabled()) {
+    // the K ranges of a tile as one cluster: partial sums travel through distributed shared memory
+    auto cluster_kernel = gemm_fewtoken_kernel<BN, OutT, EPI, true>;
+    static bool cluster_configured = false;
+    if (!cluster_configured) {
+      if (cudaFuncSetAttribute(cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_CLUSTER) != cudaSuccess)
+        return lb_last_error();
+      cluster_configured = true;
+    }
+    const int code = lb_launch_cluster(cluster_kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream,
+                                       (unsigned)splits, map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, pb.K, splits,
+                                       (float*)nullptr, (unsigned*)nullptr, false);
+    return code ? code : lb_last_error();
+  }
   const int code = lb_launch(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc,
                              pb.rows_a, pb.rows_b, pb.K, splits, splits > 1 ? pb.scratch : (float*)nullptr, pb.counters,
                              false);
