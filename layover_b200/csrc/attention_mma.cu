@@ -374,7 +374,14 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
 // ------------------------------------------------------------------------------- decode
 // Rows 0..group-1 of the 16-row tile are the query heads of one KV head (group <= 16).
-template <int MAX_DIM, bool EXACT, bool UPPER>
+// CLUSTER: the `splits` blocks of a (sequence, KV head) are one thread-block cluster (grid z =
+// cluster z = splits). Instead of writing partial results to scratch memory and leaving the merge
+// to the block that arrives last at a counter, every block owns a share of the group's outputs:
+// after a first cluster barrier (every block has left its loop, so the tile buffers are free) each
+// block sends its partial values of a share to the share's owner and its maxima and sums to
+// everyone, through distributed shared memory; after a second barrier the owners add their shares
+// in split order and store them.
+template <int MAX_DIM, bool EXACT, bool UPPER, bool CLUSTER = false>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
@@ -496,6 +503,53 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   }
   __syncthreads();
   const float c = scale_log2;
+  if (CLUSTER) {
+    const int total = group * dim, per = (total + splits - 1) / splits;
+    float* recv_acc = merge + (size_t)WARPS * 16 * mstride;            // [splits][per]: this block's share, from every split
+    float* recv_ml = recv_acc + (size_t)splits * per;                   // [splits][group][2]
+    lb_cluster_barrier();
+    for (int i = threadIdx.x; i < total; i += THREADS) {
+      const int r = i / dim, col = i % dim;
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + r) * mstride + dim]);
+      const float base = m_all == -INFINITY ? 0.f : m_all;
+      float acc = 0.f, l_all = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float* src = merge + ((size_t)w * 16 + r) * mstride;
+        const float f = fast_exp2((src[dim] - base) * c);
+        acc += src[col] * f;
+        l_all += src[dim + 1] * f;
+      }
+      const int owner = i / per;
+      lb_store_remote(lb_map_to_rank(smem_u32(recv_acc + (size_t)split * per + (i - owner * per)), owner), acc);
+      if (col == 0) {
+        for (int peer = 0; peer < splits; ++peer) {
+          const uint32_t dst = lb_map_to_rank(smem_u32(recv_ml + ((size_t)split * group + r) * 2), peer);
+          lb_store_remote(dst, m_all);
+          lb_store_remote(dst + 4, l_all);
+        }
+      }
+    }
+    lb_cluster_barrier();
+    for (int k = threadIdx.x; k < per; k += THREADS) {
+      const int i = split * per + k;
+      if (i >= total) break;
+      const int r = i / dim, col = i % dim;
+      float m_max = -INFINITY;
+      for (int s2 = 0; s2 < splits; ++s2) m_max = fmaxf(m_max, recv_ml[((size_t)s2 * group + r) * 2]);
+      const float base = m_max == -INFINITY ? 0.f : m_max;
+      float acc = 0.f, l_all = 0.f;
+      for (int s2 = 0; s2 < splits; ++s2) {
+        const float f = fast_exp2((recv_ml[((size_t)s2 * group + r) * 2] - base) * c);
+        acc += recv_acc[(size_t)s2 * per + k] * f;
+        l_all += recv_ml[((size_t)s2 * group + r) * 2 + 1] * f;
+      }
+      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(acc / l_all);
+    }
+    return;
+  }
   const unsigned tile_id = blockIdx.x * gridDim.y + blockIdx.y;
   float* my_partial = partials ? partials + ((size_t)tile_id * splits + split) * group * mstride : nullptr;
   for (int i = threadIdx.x; i < group * dim; i += THREADS) {
@@ -596,6 +650,8 @@ void configure_once() {
   allow_smem(attention_decode_kernel<128, false, true>, decode_smem(128));
   allow_smem(attention_decode_kernel<256, true, true>, decode_smem(256));
   allow_smem(attention_decode_kernel<256, false, true>, decode_smem(256));
+  allow_smem(attention_decode_kernel<128, true, false, true>, decode_smem(128));
+  allow_smem(attention_decode_kernel<128, true, true, true>, decode_smem(128));
   done = true;
 }
 
@@ -609,6 +665,21 @@ int launch_decode(int dim, int group, dim3 grid, size_t smem, cudaStream_t strea
   if (dim < 128) return lb_launch(attention_decode_kernel<128, false, true>, grid, dim3(THREADS), smem, stream, args...);
   if (dim == 256) return lb_launch(attention_decode_kernel<256, true, true>, grid, dim3(THREADS), smem, stream, args...);
   return lb_launch(attention_decode_kernel<256, false, true>, grid, dim3(THREADS), smem, stream, args...);
+}
+
+// Whether the splits of this launch can run as clusters: head size 128, 2, 4 or 8 splits, and room
+// for the received shares behind the warps' merge area.
+bool decode_cluster_fits(int dim, int group, int splits, size_t smem) {
+  if (dim != 128 || splits < 2 || splits > 8 || (splits & (splits - 1)) || !lb_cluster_reduce_enabled()) return false;
+  const size_t per = ((size_t)group * dim + splits - 1) / splits;
+  const size_t need = ((size_t)WARPS * 16 * (dim + 2) + splits * per + (size_t)splits * group * 2) * sizeof(float);
+  return need <= smem;
+}
+template <typename... Args>
+int launch_decode_cluster(int group, dim3 grid, size_t smem, cudaStream_t stream, Args... args) {
+  if (group <= 8)
+    return lb_launch_cluster(attention_decode_kernel<128, true, false, true>, grid, dim3(THREADS), smem, stream, grid.z, args...);
+  return lb_launch_cluster(attention_decode_kernel<128, true, true, true>, grid, dim3(THREADS), smem, stream, grid.z, args...);
 }
 }  // namespace
 
@@ -661,9 +732,16 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_seqs, kv_heads, splits);
-  const int code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
+  int code;
+  if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
+    code = launch_decode_cluster(q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                                  (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
-                                 q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters,
-                                 chunk_shift, page_shift);
+                                 q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, (float*)nullptr,
+                                 (unsigned*)nullptr, chunk_shift, page_shift);
+  else
+    code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
+                         (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
+                         q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters,
+                         chunk_shift, page_shift);
   return code ? code : lb_last_error();
 }

@@ -98,7 +98,37 @@ static inline int lb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
-// The same with the blocks of one z column launched as a thread-block cluster of `cluster_z` blocks.
+// Thread-block clusters: blocks that hold parts of one result are launched as one cluster and hand
+// their partial sums to one another through distributed shared memory.
+// LAYOVER_B200_CLUSTER_REDUCE=0 sends split results through scratch memory and a counter instead.
+static inline bool lb_cluster_reduce_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("LAYOVER_B200_CLUSTER_REDUCE");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
+__device__ __forceinline__ uint32_t lb_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t lb_map_to_rank(uint32_t smem_addr, uint32_t rank) {   // the same address in another block
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void lb_store_remote4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void lb_store_remote(uint32_t addr, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
+__device__ __forceinline__ void lb_cluster_barrier() {    // every thread of every block of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// A launch with the blocks of one z column as a thread-block cluster of `cluster_z` blocks.
 template <typename... KArgs, typename... Args>
 static inline int lb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     unsigned cluster_z, Args... args) {

@@ -172,25 +172,6 @@ template <int BN> struct SmallTile {
   static constexpr int SMEM_CLUSTER = SMEM + RECV_BYTES;
 };
 
-// Thread-block clusters: the blocks that hold the K ranges of one tile are launched as one cluster
-// and hand their partial sums to one another through distributed shared memory.
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {   // the same address in another block
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void store_remote4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void cluster_barrier() {    // every thread of every block of the cluster
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
 // The few-token kernel: D[i, j] = sum_k W[i, k] X[j, k] with 128 weight rows i per block, C[j, i] = D.
 // One tile (or one K range of a tile) per block, two blocks per SM, four warps that all join the
 // epilogue: for these short streams it starts and ends a few microseconds sooner than the
@@ -290,7 +271,7 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int rows_per = BM / splits;
     float* recv = reinterpret_cast<float*>(smem + T::STAGES * T::STAGE_BYTES + 256);   // [splits][rows_per][BN]
     const uint32_t owner = (uint32_t)(row / rows_per);
-    const uint32_t dst = map_to_rank(smem_u32(recv + ((size_t)split * rows_per + row % rows_per) * BN), owner);
+    const uint32_t dst = lb_map_to_rank(smem_u32(recv + ((size_t)split * rows_per + row % rows_per) * BN), owner);
     for (int c = 0; c < BN; c += 16) {
       float v[16];
       if (ready) {
@@ -300,10 +281,10 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         for (int i = 0; i < 16; ++i) v[i] = 0.f;
       }
 #pragma unroll
-      for (int i = 0; i < 16; i += 4) store_remote4(dst + (c + i) * 4, v[i], v[i + 1], v[i + 2], v[i + 3]);
+      for (int i = 0; i < 16; i += 4) lb_store_remote4(dst + (c + i) * 4, v[i], v[i + 1], v[i + 2], v[i + 3]);
     }
-    cluster_barrier();           // reached by every thread, also after a wait that ran out
-    const int first_row = m0 + (int)cluster_rank() * rows_per;
+    lb_cluster_barrier();        // reached by every thread, also after a wait that ran out
+    const int first_row = m0 + (int)lb_cluster_rank() * rows_per;
     for (int idx = threadIdx.x; idx < rows_per * valid_cols; idx += SMALL_THREADS) {
       const int j = idx / rows_per, r = idx % rows_per;
       float sum = 0.f;
@@ -873,15 +854,6 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
   const int code = lb_launch(kernel, dim3(blocks), dim3(PERSISTENT_THREADS), (size_t)T::SMEM, stream, map_a, map_b,
                              (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials, pb.counters, vector_ok);
   return code ? code : lb_last_error();
-}
-
-// LAYOVER_B200_CLUSTER_REDUCE=0 sends split products through scratch memory and a counter instead.
-static bool lb_cluster_reduce_enabled() {
-  static const bool enabled = [] {
-    const char* v = getenv("LAYOVER_B200_CLUSTER_REDUCE");
-    return !(v && v[0] == '0');
-  }();
-  return enabled;
 }
 
 template <int BN, typename OutT, int EPI = 0>

@@ -381,6 +381,21 @@ def test_attention_decode_bf16(q_heads, kv_heads, dim, page, splits):
         close(got, expected, torch.bfloat16)
 
 
+@pytest.mark.parametrize("splits", [2, 4, 8])
+@pytest.mark.parametrize("q_heads, kv_heads", [(32, 8), (16, 1), (3, 1), (2, 2), (12, 1)])
+def test_attention_decode_bf16_splits_as_clusters(q_heads, kv_heads, splits):
+    """Head size 128 with 2, 4 or 8 splits: the splits of a (sequence, KV head) run as a thread-block
+    cluster and merge through distributed shared memory; groups of 1 to 16 heads, shares of the
+    outputs that do not divide evenly, splits without a single tile (short contexts), a window."""
+    lengths = [1, 2, 17, 63, 64, 65, 127, 128, 129, 700, 1000, 257, 513]
+    for window in (0, 100):
+        for _ in range(2):
+            got, expected, _, _ = run_attention(torch.bfloat16, lengths, [1] * len(lengths), q_heads, kv_heads, 128, 16,
+                                                window=window, kernel="decode", splits=splits)
+            assert not torch.isnan(got).any()
+            close(got, expected, torch.bfloat16)
+
+
 @pytest.mark.parametrize("window", [1, 7, 64, 65, 300])
 def test_attention_decode_bf16_window(window):
     lengths = [1, 50, 64, 65, 300, 777]
