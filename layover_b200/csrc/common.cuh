@@ -98,6 +98,10 @@ static inline int lb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
+// One lane's share of a head's sum of squares: eight elements of each half, as the per-head norm
+// kernel and the fused projection epilogue both take it (the same expression, so the same bits).
+__device__ __forceinline__ float lb_square_pair(float lo, float hi) { return lo * lo + hi * hi; }
+
 // Thread-block clusters: blocks that hold parts of one result are launched as one cluster and hand
 // their partial sums to one another through distributed shared memory.
 // LAYOVER_B200_CLUSTER_REDUCE=0 sends split results through scratch memory and a counter instead.

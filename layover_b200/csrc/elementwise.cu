@@ -281,7 +281,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, T* __restrict__ q_ou
     const float* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < N; ++j) ss += lo[r][j] * lo[r][j] + hi[r][j] * hi[r][j];
+    for (int j = 0; j < N; ++j) ss += lb_square_pair(lo[r][j], hi[r][j]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
       if (o < lanes) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // whole groups agree, every lane joins

@@ -176,16 +176,37 @@ template <int BN> struct SmallTile {
 // One tile (or one K range of a tile) per block, two blocks per SM, four warps that all join the
 // epilogue: for these short streams it starts and ends a few microseconds sooner than the
 // persistent kernel below.
+// What the epilogue for fused q/k/v projections (EPI 2) needs: a 128-row tile is one head of 128
+// dims there, and the block that owns a token norms, rotates and stores the head's row of it.
+struct HeadsEpilogue {
+  const float* q_norm_w;      // [128]
+  const float* k_norm_w;
+  const float* rope_table;    // [tokens][2][64]: cos, sin
+  const int* slot_map;        // [tokens]: page * page_tokens + slot
+  bf16* q_out;                // [tokens][q_heads][128]
+  bf16* k_pool;               // [pages][kv_heads][page_tokens][128]
+  bf16* v_pool;
+  int q_heads, kv_heads, page_tokens;
+  float eps;
+};
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 // CLUSTER: the `splits` blocks of a tile are one cluster (grid z = cluster z = splits, a power of
 // two). Block r owns rows r * 128 / splits .. of the tile: every block sends those rows of its
 // accumulator into r's shared memory, and after the cluster's barrier r adds them in split order
 // and stores them. No scratch memory, fence, counter or last block: the sum starts one barrier
 // after the slowest block's last MMA.
+// EPI 2 (with CLUSTER, bf16, 128-dim heads): the product is the fused q/k/v projection of at most BN
+// tokens. Block r owns tokens r * BN / splits ..: it receives every row of those tokens, and per
+// token and head does what the per-head norm kernel does (RMSNorm of q and k heads, rotation,
+// every rounding in the same place and the sum of squares in the same order, so the bits agree),
+// then writes q to its buffer and k and v to their page. The projection never reaches memory.
 template <int BN, typename OutT, int EPI, bool CLUSTER = false>
 __global__ void __launch_bounds__(SMALL_THREADS, SmallTile<BN>::BLOCKS_PER_SM)
 gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, int K, int splits,
-                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok) {
+                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok,
+                    const HeadsEpilogue he) {
   using T = SmallTile<BN>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
@@ -258,6 +279,37 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   pdl_wait();   // the epilogue writes memory that earlier kernels may still be reading
 
   // ---------------- epilogue: every warp reads its 32 lanes of the accumulator
+  // The q/k/v epilogue gives every warp whole tokens: lane l holds features l, l + 32 (the low half of
+  // the head) and l + 64, l + 96 (their partners in the high half). What it needs per token (cos,
+  // sin, slot) and per feature (norm weight) does not depend on the product: it is read now, under
+  // the main loop, not token by token afterwards.
+  constexpr int OWNED_PER_WARP = 2;               // a block owns at most BN / 2 = 8 tokens, a warp every fourth
+  float pre_cs[OWNED_PER_WARP][2], pre_sn[OWNED_PER_WARP][2], pre_w[4] = {0.f, 0.f, 0.f, 0.f};
+  int pre_slot[OWNED_PER_WARP];
+  if (CLUSTER && EPI == 2) {
+    const int tokens_per = BN / splits, head = blockIdx.x;
+    const bool is_q = head < he.q_heads, is_k = !is_q && head < he.q_heads + he.kv_heads;
+    const float* w = is_q ? he.q_norm_w : (is_k ? he.k_norm_w : nullptr);
+    if (w) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) pre_w[e] = w[lane + 32 * e];
+    }
+#pragma unroll
+    for (int i = 0; i < OWNED_PER_WARP; ++i) {
+      const int jj = warp + 4 * i, token = blockIdx.y * BN + (int)blockIdx.z * tokens_per + jj;
+      pre_cs[i][0] = pre_cs[i][1] = 1.f; pre_sn[i][0] = pre_sn[i][1] = 0.f; pre_slot[i] = 0;
+      if (jj < tokens_per && token < rows_b) {
+        if (w) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            pre_cs[i][e] = round_bf16(he.rope_table[((size_t)token * 2) * 64 + lane + 32 * e]);
+            pre_sn[i][e] = round_bf16(he.rope_table[((size_t)token * 2 + 1) * 64 + lane + 32 * e]);
+          }
+        }
+        if (!is_q) pre_slot[i] = he.slot_map[token];
+      }
+    }
+  }
   const bool ready = mbar_wait(tmem_full, 0);
   if (!ready) { atomicCAS(&g_gemm_error, 0, 3); flag[0] = 1; }
   fence_after_sync();
@@ -267,7 +319,89 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
   float* my_partial = (partials && !CLUSTER) ? partials + ((size_t)tile_id * splits + split) * BN * BM : nullptr;
 
-  if (CLUSTER) {
+  if (CLUSTER && EPI == 2) {
+    const int tokens_per = BN / splits;
+    float* recv = reinterpret_cast<float*>(smem + T::STAGES * T::STAGE_BYTES + 256);   // [splits][128][tokens_per]
+    // send: this row's values of the tokens that a block owns are neighbours there
+    for (int c = 0; c < BN; c += 16) {
+      if (c >= valid_cols) break;                                    // the same for the whole block
+      float v[16];
+      if (ready) {
+        tmem_ld16(lane_base + c, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      }
+      if (tokens_per % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          const int j = c + i;
+          if (j < valid_cols)
+            lb_store_remote4(lb_map_to_rank(smem_u32(recv + ((size_t)split * BM + row) * tokens_per + j % tokens_per),
+                                            (uint32_t)(j / tokens_per)), v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int j = c + i;
+          if (j < valid_cols)
+            lb_store_remote(lb_map_to_rank(smem_u32(recv + ((size_t)split * BM + row) * tokens_per + j % tokens_per),
+                                           (uint32_t)(j / tokens_per)), v[i]);
+        }
+      }
+    }
+    lb_cluster_barrier();        // reached by every thread, also after a wait that ran out
+    const int head = blockIdx.x;
+    const bool is_q = head < he.q_heads, is_k = !is_q && head < he.q_heads + he.kv_heads;
+#pragma unroll
+    for (int i = 0; i < OWNED_PER_WARP; ++i) {
+      const int jj = warp + 4 * i, token = n0 + (int)lb_cluster_rank() * tokens_per + jj;
+      if (jj >= tokens_per || token >= rows_b) break;                // the same for the whole warp
+      float x[4];                                                    // features lane, +32, +64, +96
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float sum = 0.f;
+        for (int sp = 0; sp < splits; ++sp) sum += recv[((size_t)sp * BM + lane + 32 * e) * tokens_per + jj];
+        x[e] = round_bf16(sum);                                      // the projection's own rounding
+      }
+      if (is_q || is_k) {
+        // The sum of squares in the order of the per-head kernel: eight lanes of eight (low, high)
+        // pairs each, one after the other, then a butterfly over the eight partial sums. Pair
+        // (x[0], x[2]) is pair lane % 8 of partial sum lane / 8, pair (x[1], x[3]) of partial sum lane / 8 + 4.
+        const float sq_a = lb_square_pair(x[0], x[2]), sq_b = lb_square_pair(x[1], x[3]);
+        float part_a = 0.f, part_b = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          part_a += __shfl_sync(0xffffffffu, sq_a, (lane & 24) + j);
+          part_b += __shfl_sync(0xffffffffu, sq_b, (lane & 24) + j);
+        }
+        const float pair_sum = part_a + part_b;                      // p[g] + p[g + 4], g = lane / 8
+        const float ss = (__shfl_sync(0xffffffffu, pair_sum, 0) + __shfl_sync(0xffffffffu, pair_sum, 16)) +
+                         (__shfl_sync(0xffffffffu, pair_sum, 8) + __shfl_sync(0xffffffffu, pair_sum, 24));
+        const float inv = 1.0f / sqrtf(ss / (float)BM + he.eps);
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = round_bf16(pre_w[e] * round_bf16(x[e] * inv));
+        // rotate_half(x) = (-hi, lo): each product and the sum round to bfloat16
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float cs = pre_cs[i][e], sn = pre_sn[i][e];
+          x[e] = round_bf16(round_bf16(y[e] * cs) + round_bf16(-y[e + 2] * sn));
+          x[e + 2] = round_bf16(round_bf16(y[e + 2] * cs) + round_bf16(y[e] * sn));
+        }
+      }
+      bf16* dst;
+      if (is_q) {
+        dst = he.q_out + ((size_t)token * he.q_heads + head) * BM;
+      } else {
+        const int kvh = is_k ? head - he.q_heads : head - he.q_heads - he.kv_heads;
+        const size_t page = pre_slot[i] / he.page_tokens, within = pre_slot[i] % he.page_tokens;
+        dst = (is_k ? he.k_pool : he.v_pool) + ((page * he.kv_heads + kvh) * he.page_tokens + within) * BM;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dst[lane + 32 * e] = __float2bfloat16_rn(x[e]);
+    }
+  } else if (CLUSTER) {
     const int rows_per = BM / splits;
     float* recv = reinterpret_cast<float*>(smem + T::STAGES * T::STAGE_BYTES + 256);   // [splits][rows_per][BN]
     const uint32_t owner = (uint32_t)(row / rows_per);
@@ -896,12 +1030,38 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
     }
     const int code = lb_launch_cluster(cluster_kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream,
                                        (unsigned)splits, map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, pb.K, splits,
-                                       (float*)nullptr, (unsigned*)nullptr, false);
+                                       (float*)nullptr, (unsigned*)nullptr, false, HeadsEpilogue{});
     return code ? code : lb_last_error();
   }
   const int code = lb_launch(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc,
                              pb.rows_a, pb.rows_b, pb.K, splits, splits > 1 ? pb.scratch : (float*)nullptr, pb.counters,
-                             false);
+                             false, HeadsEpilogue{});
+  return code ? code : lb_last_error();
+}
+
+// The fused q/k/v projection of at most 16 tokens with 128-dim heads: returns 1 when the sizes do
+// not allow it (nothing is launched then and the caller runs the product and the norm kernel).
+int launch_heads(const CUtensorMap& map_a, const CUtensorMap& map_b, const Problem& pb, const HeadsEpilogue& he,
+                 cudaStream_t stream) {
+  constexpr int BN = 16;
+  using T = SmallTile<BN>;
+  const int tiles = (pb.rows_a + BM - 1) / BM, total_kb = (pb.K + BK - 1) / BK;
+  int splits = (pb.sm_count + tiles - 1) / tiles;
+  if (splits > 8) splits = 8;
+  if (splits > total_kb / 4) splits = total_kb / 4;           // at least four K blocks per split
+  while (splits & (splits - 1)) splits &= splits - 1;         // down to a power of two
+  if (splits < 2 || !lb_cluster_reduce_enabled()) return 1;
+  auto kernel = gemm_fewtoken_kernel<BN, bf16, 2, true>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_CLUSTER) != cudaSuccess)
+      return lb_last_error();
+    configured = true;
+  }
+  dim3 grid(tiles, 1, splits);
+  const int code = lb_launch_cluster(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream, (unsigned)splits,
+                                     map_a, map_b, (bf16*)nullptr, 0L, pb.rows_a, pb.rows_b, pb.K, splits, (float*)nullptr,
+                                     (unsigned*)nullptr, false, he);
   return code ? code : lb_last_error();
 }
 }  // namespace
@@ -994,4 +1154,28 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
   LB_GEMM_CASE(256, false)
 #undef LB_GEMM_CASE
   return LB_ERR_SIZE;
+}
+
+// The q/k/v projection of `M` <= 16 tokens fused with the per-head norm, the rotation and the page
+// write: W [(q_heads + 2 kv_heads) * 128, K] stacked q, k, v; what `lb_gemm_tcgen05` followed by the
+// per-head norm kernel would leave in q_out and the pools, bit for bit. Returns 0 when launched,
+// 1 when these sizes are not taken (head size other than 128, more than 16 tokens, too few K blocks
+// to split, clusters switched off): nothing has been launched then.
+LB_EXPORT int lb_gemm_qkv_heads(const void* A, const void* W, int M, int K, long lda, long ldw, int q_heads, int kv_heads,
+                                int head_dim, const float* q_norm_w, const float* k_norm_w, const float* rope_table,
+                                int n_freq, const int* slot_map, void* q_out, void* k_pool, void* v_pool, int page_tokens,
+                                float eps, int sm_count, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (head_dim != BM || M > 16 || n_freq * 2 != head_dim || !q_norm_w || !k_norm_w || !rope_table || !slot_map || !q_out ||
+      !k_pool || !v_pool || q_heads < 1 || kv_heads < 1 || page_tokens < 1)
+    return 1;
+  if (!lb_gemm_tcgen05_supports(A, W, K, lda, ldw)) return 1;
+  if (sm_count < 1) sm_count = 1;
+  const int rows = (q_heads + 2 * kv_heads) * head_dim;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, W, rows, K, ldw, BM) || !make_map(&map_b, A, M, K, lda, 16)) return 1;
+  const Problem pb{rows, M, K, 16, true, sm_count, 0, nullptr, 0, nullptr, 0};
+  const HeadsEpilogue he{q_norm_w, k_norm_w, rope_table, slot_map, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool,
+                         q_heads, kv_heads, page_tokens, eps};
+  return launch_heads(map_a, map_b, pb, he, stream);
 }

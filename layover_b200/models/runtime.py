@@ -58,6 +58,7 @@ def make_runtime(dtype: torch.dtype, device: torch.device | str) -> Runtime:
         runtime = Runtime(dtype, device, _linear_bf16)
         runtime.attention = ops.attention_bf16
         runtime.linear_swiglu = _linear_swiglu_bf16
+        runtime.linear_heads = ops.gemm_qkv_heads
         runtime.swiglu_block = ops.SWIGLU_BLOCK
         runtime.interleave_gate_up = ops.interleave_gate_up
         runtime.tile_sizes = ops.attention_bf16_tile_sizes()

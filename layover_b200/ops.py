@@ -303,6 +303,38 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, max_splits
     return out
 
 
+def gemm_qkv_heads(h: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   q_norm_w: torch.Tensor, k_norm_w: torch.Tensor, table: torch.Tensor, slot_map: torch.Tensor,
+                   q_heads: int, kv_heads: int, dim: int, page_tokens: int, eps: float) -> bool:
+    """The stacked q/k/v projection of up to 16 tokens with the per-head norm, the rotation and the
+    page write in its epilogue (head size 128): leaves in q_out and the pools what `gemm_tcgen05`
+    followed by `qk_norm_rope_kv` leaves there, bit for bit. False: these sizes are not taken and
+    nothing was launched."""
+    tokens = h.shape[0]
+    if (dim != 128 or tokens > 16 or h.dtype != torch.bfloat16 or q_norm_w is None or k_norm_w is None or table is None
+            or k_pool is None or not gemm_tcgen05_supports(h, w_qkv)):
+        return False
+    for name, t in (("h", h), ("w_qkv", w_qkv), ("q_out", q_out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _need(t, torch.bfloat16, name)
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("table", table)):
+        _need(t, torch.float32, name)
+    _need(slot_map, torch.int32, "slot_map")
+    if w_qkv.shape != ((q_heads + 2 * kv_heads) * dim, h.shape[1]) or tuple(table.shape) != (tokens, 2, dim // 2) \
+            or q_out.shape != (tokens, q_heads * dim) or not q_out.is_contiguous():
+        raise ValueError("gemm_qkv_heads: shapes do not agree")
+    sms = gemm_scratch(h.device)[2]
+    fn = _fn("gemm_tcgen05", "lb_gemm_qkv_heads",
+             [c_void_p, c_void_p, c_int, c_int, c_long, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p])
+    code = fn(_ptr(h), _ptr(w_qkv), tokens, h.shape[1], h.stride(0), w_qkv.stride(0), q_heads, kv_heads, dim,
+              _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table), table.shape[2], _ptr(slot_map), _ptr(q_out), _ptr(k_pool),
+              _ptr(v_pool), page_tokens, float(eps), sms, _stream())
+    if code == 1:
+        return False
+    _check(code, "gemm_qkv_heads")
+    return True
+
+
 def gemm_status() -> int:
     """0, or the code a tensor-core product recorded when one of its bounded waits ran out
     (1 loads, 2 MMAs, 3 epilogue). Synchronises; clears the code."""

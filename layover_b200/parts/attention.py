@@ -85,12 +85,19 @@ class Attention(Part):
         tokens = h.shape[0]
         own_kv = 0 if self.shares_cache else self.kv_heads
         group = batch.groups[cache.group]
-        qkv = self.runtime.linear(h, self.w_qkv)
         q = torch.empty((tokens, self.q_heads * self.dim), dtype=h.dtype, device=h.device)
         eps = float(self.qk_norm_eps or 0.0)
         table = self.position.tables(batch) if self.position is not None else None
         fused = self.position is None or table is not None
         k_pool, v_pool = (cache.k_pool, cache.v_pool) if own_kv else (None, None)
+        heads = self.runtime.linear_heads
+        if (heads is not None and own_kv and table is not None and self.qk_norm_eps is not None
+                and heads(h, self.w_qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, group.slot_map,
+                          self.q_heads, own_kv, self.dim, cache.page_tokens, eps)):
+            out = torch.empty_like(q)      # projection, norm, rotation and page write were one kernel
+            self.attend(q, cache, batch, group, out)
+            return self.runtime.linear(out, self.w_o)
+        qkv = self.runtime.linear(h, self.w_qkv)
         if fused:
             ops.qk_norm_rope_kv(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, group.slot_map,
                                 self.q_heads, own_kv, self.dim, cache.page_tokens, eps)

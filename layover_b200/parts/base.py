@@ -67,6 +67,10 @@ class Runtime:
     # linear_swiglu(a, w_interleaved) -> silu(gate) * up or None; w made by interleave_gate_up(gate, up)
     linear_swiglu: Callable[..., torch.Tensor | None] | None = None
     interleave_gate_up: Callable[..., torch.Tensor] | None = None
+    # linear_heads(h, w_qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, table, slot_map, q_heads, kv_heads, dim,
+    #              page_tokens, eps) -> bool: the stacked q/k/v projection with the per-head norm, the rotation
+    #              and the page write in its epilogue; False (nothing done) where the run or the sizes have none
+    linear_heads: Callable[..., bool] | None = None
     swiglu_block: int = 0                 # the fused product wants the width to be a multiple of this
     tile_sizes: tuple[int, ...] = ()      # query-tile sizes whose tile lists the batch must carry
     kernel_libraries: tuple[str, ...] = ()  # what has to be compiled before the first step

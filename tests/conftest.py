@@ -25,9 +25,11 @@ TINY = {
               rms_norm_eps=1e-5, tie_word_embeddings=False),
 }
 # Two more with the head size of the served models, the only one the tensor-core attention takes:
-# "c" has an even number of query heads per KV head (two heads per block), "d" an odd one.
+# "c" has an even number of query heads per KV head (two heads per block) and is wide enough for the
+# split products whose blocks form clusters (the fused q/k/v projection of decode steps); "d" has an
+# odd number of heads per KV head and a narrow width.
 TINY.update({
-    "c": dict(vocab_size=384, hidden_size=256, intermediate_size=320, num_hidden_layers=2, num_attention_heads=4,
+    "c": dict(vocab_size=384, hidden_size=512, intermediate_size=320, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, head_dim=128, max_position_embeddings=512, rope_theta=1000000.0,
               rms_norm_eps=1e-6, tie_word_embeddings=False),
     "d": dict(vocab_size=320, hidden_size=192, intermediate_size=256, num_hidden_layers=2, num_attention_heads=3,

@@ -426,6 +426,46 @@ def test_bf16_attention_finds_one_far_key_among_thousands(kernel, far_key):
     assert (out.float().cpu() - 7.0).abs().max() < 0.05
 
 
+@pytest.mark.parametrize("tokens", [1, 3, 8, 16])
+@pytest.mark.parametrize("q_heads, kv_heads, hidden", [(32, 8, 2560), (4, 2, 1024), (3, 1, 512), (16, 8, 1024)])
+def test_fused_qkv_projection_equals_product_then_head_kernel(q_heads, kv_heads, hidden, tokens):
+    """The q/k/v projection with norm, rotation and page write in its epilogue leaves the same bits in
+    the query buffer and the pages as the product followed by the per-head kernel."""
+    o = ops()
+    dim, page, pages = 128, 16, 9
+    gen = torch.Generator().manual_seed(tokens * 1000 + q_heads)
+    rows = (q_heads + 2 * kv_heads) * dim
+    h = torch.randn(tokens, hidden, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(rows, hidden, generator=gen) / math.sqrt(hidden)).to(torch.bfloat16).cuda()
+    q_w = (1 + 0.2 * torch.randn(dim, generator=gen)).cuda()
+    k_w = (1 + 0.2 * torch.randn(dim, generator=gen)).cuda()
+    positions = torch.randint(0, 4000, (tokens,), generator=gen).to(torch.int32).cuda()
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, dim, 2).float() / dim))).cuda()
+    table = torch.empty(tokens, 2, dim // 2, dtype=torch.float32, device="cuda")
+    o.rope_table(positions, inv_freq, table)
+    slots = torch.randperm(pages * page, generator=gen)[:tokens].to(torch.int32).cuda()
+
+    def pools():
+        return (torch.zeros(pages, kv_heads, page, dim, dtype=torch.bfloat16, device="cuda"),
+                torch.zeros(pages, kv_heads, page, dim, dtype=torch.bfloat16, device="cuda"))
+
+    k1, v1 = pools()
+    qkv = torch.empty(tokens, rows, dtype=torch.bfloat16, device="cuda")
+    o.gemm_tcgen05(h, w, qkv)
+    q1 = torch.empty(tokens, q_heads * dim, dtype=torch.bfloat16, device="cuda")
+    o.qk_norm_rope_kv(qkv, q1, k1, v1, q_w, k_w, table, slots, q_heads, kv_heads, dim, page, 1e-6)
+    k2, v2 = pools()
+    q2 = torch.full_like(q1, float("nan"))
+    for _ in range(2):
+        taken = o.gemm_qkv_heads(h, w, q2, k2, v2, q_w, k_w, table, slots, q_heads, kv_heads, dim, page, 1e-6)
+    assert o.gemm_status() == 0
+    if not taken:
+        assert hidden // 64 < 8 or rows // 128 >= 148      # too few K blocks to split, or nothing to split for
+        return
+    assert torch.equal(q1, q2)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+
+
 @pytest.mark.parametrize("m, inter, k", [(1, 64, 64), (8, 9728, 2560), (17, 128, 96), (64, 192, 200), (128, 1024, 256),
                                          (129, 64, 64), (300, 448, 136), (2048, 1280, 512), (2048, 9728, 256)])
 def test_gemm_tcgen05_swiglu_epilogue(m, inter, k):
