@@ -13,6 +13,7 @@ from ..weights.random_init import random_tensors
 from . import qwen3  # noqa: F401  (registers the architecture)
 from .model import Model, assemble
 from .runtime import make_runtime
+from ..parts.base import PartSpec
 from .spec import LayerSpec, ModelSpec, ScheduleEntry
 
 DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp32": torch.float32, "float32": torch.float32}
@@ -33,9 +34,36 @@ def spec_for_config(config) -> ModelSpec:
     return arch.build_spec(config)
 
 
+def _head_sizes(value) -> set[int]:
+    """Every `head_dim` found in a tree of part specifications."""
+    found: set[int] = set()
+    if isinstance(value, PartSpec):
+        found |= _head_sizes(value.params)
+    elif isinstance(value, dict):
+        for key, item in value.items():
+            if key == "head_dim" and isinstance(item, int):
+                found.add(item)
+            else:
+                found |= _head_sizes(item)
+    elif isinstance(value, (list, tuple)):
+        for item in value:
+            found |= _head_sizes(item)
+    return found
+
+
+def _build_for(spec: ModelSpec, runtime) -> None:
+    """Compile what this model needs before its first step: the run's kernel libraries, without the
+    tensor-core attention when no layer has the head size it takes (it would still be compiled at
+    first use)."""
+    names = list(runtime.kernel_libraries)
+    if "attention_tcgen05" in names and 128 not in _head_sizes([layer.block for layer in spec.layers]):
+        names.remove("attention_tcgen05")
+    _build.ensure_built(names)
+
+
 def _finish(spec: ModelSpec, config, tensors, dtype, device) -> Model:
     runtime = make_runtime(dtype, device)
-    _build.ensure_built(runtime.kernel_libraries)
+    _build_for(spec, runtime)
     return assemble(spec, config).bind(tensors, runtime)
 
 
@@ -46,7 +74,7 @@ def load_model(name_or_path: str | Path, device: torch.device | str = "cuda", dt
     arch, config = load_config(name_or_path)
     spec = arch.build_spec(config)
     runtime = make_runtime(dtype, device)       # refuses a CPU before anything is read
-    _build.ensure_built(runtime.kernel_libraries)
+    _build_for(spec, runtime)
     model = assemble(spec, config)
     tensors = load_tensors(name_or_path, model.tensor_specs(), dtype, device, set(spec.ignorable_tensors))
     return model.bind(tensors, runtime)
@@ -58,7 +86,7 @@ def random_model(config, seed: int = 0, device: torch.device | str = "cuda", dty
     dtype, device = as_dtype(dtype), torch.device(device)
     spec = spec_for_config(config)
     runtime = make_runtime(dtype, device)
-    _build.ensure_built(runtime.kernel_libraries)
+    _build_for(spec, runtime)
     model = assemble(spec, config)
     tensors = random_tensors(model.tensor_specs(), seed, dtype, device, std, norm_std)
     return model.bind(tensors, runtime)
