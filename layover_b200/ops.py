@@ -391,25 +391,31 @@ def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, t
 
 
 def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> int:
-    """How many ways to split the context so that about two blocks per SM are in flight.
+    """How many ways to split the context of a decode step.
 
-    With head size 128 the kernel runs 2, 4 or 8 splits as a thread-block cluster that merges through
-    distributed shared memory, which costs a few microseconds less than the merge through scratch
-    memory: there the count is a power of two up to 8 unless a long context wants many more blocks
-    (measured at 3,072 keys: 8 splits 10.3 us against 16 splits 11.7 us for one sequence, 15.7 against
-    20.2 us for four; at 32,768 keys one sequence wants 32: 37 us against 90 us with 8)."""
+    A block is one (sequence, KV head, split), two blocks fit an SM, and the blocks run in rounds of
+    2 x SMs. With head size 128 the kernel runs 2, 4 or 8 splits as a thread-block cluster that merges
+    through distributed shared memory; more splits merge through scratch memory, which costs more.
+    The count is the one with the lowest estimate rounds x (64-key tiles per split + overhead in
+    tiles): 4 for a cluster, 10 for the scratch merge. That fits what was measured at 3,072 keys
+    (sequences: best splits) 1: 8, 4: 8, 8: 4, 16: 2, 24: 4, 32: 1, 40: 4, 48: 2, 64: 1, 128: 2, and one
+    sequence of 32,768 keys: 32 or more through scratch memory."""
     natural = n_seqs * kv_heads
     want = max(1, 2 * sm_count // natural)                    # all blocks resident at once, two per SM
     splits = min(want, 128, max(1, max_context // 192))       # at least three 64-key tiles per split
-    if dim == 128:
-        clustered = min(want, max(1, max_context // 128))     # two tiles per split are worth a cluster
-        if clustered >= 8 and (clustered <= 11 or max_context <= 8192):
-            return 8
-        if clustered < 8:
-            return 1 << (clustered.bit_length() - 1)
     while splits > 1 and n_seqs * q_heads * splits * (dim + 2) > _ATTN_SCRATCH_FLOATS:
         splits -= 1
-    return splits
+    if dim != 128:
+        return splits
+    slots, tiles = 2 * sm_count, max(1, -(-max_context // 64))
+
+    def estimate(count: int, overhead: int) -> int:
+        return -(-natural * count // slots) * (-(-tiles // count) + overhead)
+
+    best = min((c for c in (1, 2, 4, 8) if c <= tiles), key=lambda c: (estimate(c, 4), c))
+    if splits > 8 and estimate(splits, 10) < estimate(best, 4):
+        return splits
+    return best
 
 
 def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, seq_list, n_seqs, q_heads, kv_heads, dim,
