@@ -69,6 +69,13 @@ class StepBatch:
     device_tokens: bool          # whether any token comes from the device
     groups: list[GroupBatch]
     tiles: dict[int, QueryTiles]
+    # a mixed step (prompt portions beside single tokens) also lists the two kinds apart, so that the
+    # single tokens can go through the decode kernels: the sequences with one token, and the query
+    # tiles of the others
+    decode_seqs: torch.Tensor | None
+    n_decode_seqs: int
+    decode_max_ctx: int
+    portion_tiles: dict[int, QueryTiles]
     # host-side facts for planning launches
     q_lens: list[int]
     ctx_lens: list[int]
@@ -155,6 +162,15 @@ class BatchBuilder:
             tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, size)]
             tile_lists[size] = tiles
             layout.add(f"tile_seq{size}", len(tiles)); layout.add(f"tile_q0{size}", len(tiles))
+        singles = [s for s, n in enumerate(q_lens) if n == 1]
+        mixed = 0 < len(singles) < n_seqs
+        portion_lists = {}
+        if mixed:
+            layout.add("decode_seqs", len(singles))
+            for size in self.tile_sizes:
+                tiles = [(s, q0) for s, n in enumerate(q_lens) if n > 1 for q0 in range(0, n, size)]
+                portion_lists[size] = tiles
+                layout.add(f"ptile_seq{size}", len(tiles)); layout.add(f"ptile_q0{size}", len(tiles))
 
         host, ring_index = self._pinned(layout.size)
         view = host.numpy()
@@ -207,6 +223,10 @@ class BatchBuilder:
             put(f"slots{g}", slots)
         for size, tiles in tile_lists.items():
             put(f"tile_seq{size}", [t[0] for t in tiles]); put(f"tile_q0{size}", [t[1] for t in tiles])
+        if mixed:
+            put("decode_seqs", singles)
+            for size, tiles in portion_lists.items():
+                put(f"ptile_seq{size}", [t[0] for t in tiles]); put(f"ptile_q0{size}", [t[1] for t in tiles])
 
         if device_buffer is not None:
             if device_buffer.numel() < layout.size:
@@ -235,6 +255,10 @@ class BatchBuilder:
             groups=[GroupBatch(get(f"table{g}"), get(f"slots{g}")) for g in range(len(cache.paged))],
             tiles={size: QueryTiles(get(f"tile_seq{size}"), get(f"tile_q0{size}"), len(tiles))
                    for size, tiles in tile_lists.items()},
+            decode_seqs=get("decode_seqs") if mixed else None, n_decode_seqs=len(singles) if mixed else 0,
+            decode_max_ctx=max((ctx_lens[s] for s in singles), default=0) if mixed else 0,
+            portion_tiles={size: QueryTiles(get(f"ptile_seq{size}"), get(f"ptile_q0{size}"), len(tiles))
+                           for size, tiles in portion_lists.items()},
             q_lens=q_lens, ctx_lens=ctx_lens, max_q_len=max(q_lens), max_ctx=max(ctx_lens),
             all_decode=max(q_lens) == 1, real_seqs=real,
         )

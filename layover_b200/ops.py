@@ -514,7 +514,7 @@ def attention_bf16_tile_sizes() -> tuple[int, ...]:
 def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
     """The bfloat16 path's attention for one step: prompt portions go through the tcgen05 tile kernel
     where it takes the sizes (head size 128, pages of 8..128 tokens), else through the mma.sync
-    one; steps of single tokens go through the split decode kernel."""
+    one; single tokens, alone or beside prompt portions, go through the split decode kernel."""
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
         # the widest context the block table can describe (what a captured step may later see)
@@ -522,11 +522,20 @@ def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, pa
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, None,
                               batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits)
         return
+    tiles_of = batch.tiles
+    if batch.n_decode_seqs > 0 and q_heads // kv_heads <= 16:
+        # a mixed step: the sequences with a single token go through the decode kernel (a tile kernel
+        # would spend a whole tile of queries on each), the prompt portions through the tile kernel
+        sms = gemm_scratch(q.device)[2]
+        splits = decode_splits(batch.n_decode_seqs, q_heads, kv_heads, dim, batch.decode_max_ctx, sms)
+        attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, batch.decode_seqs,
+                              batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits)
+        tiles_of = batch.portion_tiles
     if cache.pool is not None and attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens):
-        tiles = batch.tiles[TCGEN05_TILE]
+        tiles = tiles_of[TCGEN05_TILE]
         attention_tcgen05_prefill(q, cache.pool, cache.layer, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq,
                                   tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
         return
-    tiles = batch.tiles[attention_mma_block_queries()]
+    tiles = tiles_of[attention_mma_block_queries()]
     attention_prefill_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq,
                            tiles.tile_q0, tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)

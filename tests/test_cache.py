@@ -181,6 +181,27 @@ def test_batch_descriptors():
         BatchBuilder(m, "cpu").build([StepEntry(a, [1], [1])])
 
 
+def test_a_mixed_step_lists_single_tokens_and_portions_apart():
+    m = manager([FULL], blocks=20, page=4, device="cpu")
+    a, b, c, d = (m.open(name) for name in "abcd")
+    for seq, held in ((a, 6), (c, 9)):
+        m.grow(seq, held); m.commit(seq, held)
+    entries = [StepEntry(a, [7], [0]), StepEntry(b, [1] * 5, [4]), StepEntry(c, [2], [0]), StepEntry(d, [3, 4], [])]
+    for e in entries:
+        m.grow(e.seq, e.seq.num_tokens + len(e.tokens))
+    batch = BatchBuilder(m, "cpu", (2, 4)).build(entries)
+    assert not batch.all_decode and batch.n_decode_seqs == 2 and batch.decode_seqs.tolist() == [0, 2]
+    assert batch.decode_max_ctx == 10
+    tiles = batch.portion_tiles[2]
+    assert list(zip(tiles.tile_seq.tolist(), tiles.tile_q0.tolist())) == [(1, 0), (1, 2), (1, 4), (3, 0)]
+    assert batch.portion_tiles[4].count == 3 and batch.tiles[2].count == 6
+    # steps of one kind have nothing to tell apart
+    only_portions = BatchBuilder(m, "cpu", (2,)).build([StepEntry(b, [5, 5], [])])
+    assert only_portions.n_decode_seqs == 0 and only_portions.decode_seqs is None and not only_portions.portion_tiles
+    only_singles = BatchBuilder(m, "cpu", (2,)).build([StepEntry(a, [5], [0]), StepEntry(c, [5], [0])])
+    assert only_singles.all_decode and only_singles.n_decode_seqs == 0
+
+
 def test_fixed_capacity_batches_pad_onto_the_scratch_page():
     m = manager([FULL], blocks=10, page=4, device="cpu")
     a = m.open("a")
