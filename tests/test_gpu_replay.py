@@ -82,6 +82,35 @@ def test_every_cut_at_the_served_head_size(tiny_folders, tmp_path, name, cut):
     compare(rows, expected_rows(tiny_folders, name, "bfloat16"), torch.bfloat16)
 
 
+SERVED_SHAPES = {   # (hidden, intermediate, query heads, KV heads) of the family's sizes, head size 128
+    "0.6b": (1024, 3072, 16, 8), "4b": (2560, 9728, 32, 8), "14b": (5120, 17408, 40, 8), "32b": (5120, 25600, 64, 8),
+}
+
+
+@pytest.mark.parametrize("size", list(SERVED_SHAPES))
+def test_one_layer_of_each_served_size(tmp_path, size):
+    """The kernels at the family's real layer sizes (one layer, a small vocabulary): a prompt whole,
+    its last tokens one by one, and two more requests decoding beside it, in bfloat16."""
+    from safetensors.torch import load_file
+
+    import layover_b200 as lb
+
+    hidden, inter, q_heads, kv_heads = SERVED_SHAPES[size]
+    config = lb.Qwen3Config(vocab_size=640, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=1,
+                            num_attention_heads=q_heads, num_key_value_heads=kv_heads, head_dim=128,
+                            max_position_embeddings=1024, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                            tie_word_embeddings=True)
+    folder = tmp_path / "model"
+    lb.write_model_folder(config, folder, seed=5, std=0.02, norm_std=0.1)
+    raw = json.loads((folder / "config.json").read_text())
+    weights = load_file(str(folder / "model.safetensors"))
+    requests = {f"r{i}": random_prompt(640, n, seed=900 + i) for i, n in enumerate([150, 9, 40])}
+    expected = {rid: plain_forward(raw, weights, tokens, torch.bfloat16).numpy() for rid, tokens in requests.items()}
+    for cut in ("tail", "mixed"):
+        rows = run_trace(folder, "bfloat16", CUTS[cut](requests), tmp_path / cut, block_tokens=16)
+        compare(rows, expected, torch.bfloat16)
+
+
 @pytest.mark.parametrize("name", ["a", "b"])
 def test_32bit_logits_do_not_depend_on_the_cut_at_all(tiny_folders, tmp_path, name):
     """In the 32-bit path every sum has a fixed order, so cutting changes no bit."""
