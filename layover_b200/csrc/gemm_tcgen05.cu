@@ -205,8 +205,7 @@ template <int BN, typename OutT, int EPI, bool CLUSTER = false>
 __global__ void __launch_bounds__(SMALL_THREADS, SmallTile<BN>::BLOCKS_PER_SM)
 gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, int K, int splits,
-                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok,
-                    const HeadsEpilogue he) {
+                    float* __restrict__ partials, unsigned* __restrict__ counters, const HeadsEpilogue he) {
   using T = SmallTile<BN>;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
@@ -450,22 +449,11 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               store_one<OutT>(C + (size_t)(n0 + c + i) * ldc + (m0 >> 1) + row, swiglu_bf16(v[i], handover[row * 17 + i]));
         }
         __syncthreads();
-      } else if (true) {
+      } else {
         if (m0 + row < rows_a) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (c + i < valid_cols) store_one<OutT>(C + (size_t)(n0 + c + i) * ldc + m0 + row, v[i]);
-        }
-      } else {
-        if (m0 + row < rows_a) {
-          OutT* dst = C + (size_t)(m0 + row) * ldc + n0 + c;
-          if (vector_ok && c + 16 <= valid_cols) {
-            store_row16<OutT>(dst, v);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (c + i < valid_cols) store_one<OutT>(dst + i, v[i]);
-          }
         }
       }
     }
@@ -507,8 +495,7 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             if (j0 + u < valid_cols) {
-              if (true) store_one<OutT>(C + (size_t)(n0 + j0 + u) * ldc + m0 + row, sum[u]);
-              else store_one<OutT>(C + (size_t)(m0 + row) * ldc + n0 + j0 + u, sum[u]);
+              store_one<OutT>(C + (size_t)(n0 + j0 + u) * ldc + m0 + row, sum[u]);
             }
           }
         }
@@ -1030,12 +1017,12 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
     }
     const int code = lb_launch_cluster(cluster_kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream,
                                        (unsigned)splits, map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, pb.K, splits,
-                                       (float*)nullptr, (unsigned*)nullptr, false, HeadsEpilogue{});
+                                       (float*)nullptr, (unsigned*)nullptr, HeadsEpilogue{});
     return code ? code : lb_last_error();
   }
   const int code = lb_launch(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc,
                              pb.rows_a, pb.rows_b, pb.K, splits, splits > 1 ? pb.scratch : (float*)nullptr, pb.counters,
-                             false, HeadsEpilogue{});
+                             HeadsEpilogue{});
   return code ? code : lb_last_error();
 }
 
@@ -1061,7 +1048,7 @@ int launch_heads(const CUtensorMap& map_a, const CUtensorMap& map_b, const Probl
   dim3 grid(tiles, 1, splits);
   const int code = lb_launch_cluster(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream, (unsigned)splits,
                                      map_a, map_b, (bf16*)nullptr, 0L, pb.rows_a, pb.rows_b, pb.K, splits, (float*)nullptr,
-                                     (unsigned*)nullptr, false, he);
+                                     (unsigned*)nullptr, he);
   return code ? code : lb_last_error();
 }
 }  // namespace
