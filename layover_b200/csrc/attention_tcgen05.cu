@@ -1,27 +1,26 @@
-// Paged grouped-query attention for bfloat16 on the 5th-generation tensor cores: both products of
-// attention (S = Q K^T and O = P V) are tcgen05.mma with accumulators in tensor memory, K and V
-// pages come by TMA straight from the block table, and the softmax runs one thread per query row.
-// The reference gathers the history out of its pool and calls a library kernel for prompts
-// (layover/model.py:84-90) and a Triton program per (sequence, head) for decode
-// (layover/kernels/triton_decode.py:39-119).
+// Paged grouped-query attention for prompt portions in bfloat16 on the 5th-generation tensor cores:
+// both products of attention (S = Q K^T and O = P V) are tcgen05.mma with accumulators in tensor
+// memory, K and V pages come by TMA straight from the block table, and the softmax runs one thread
+// per query row. The reference gathers the history out of its pool and calls a library kernel for
+// prompts (layover/model.py:84-90).
 //
-// One kernel, two row mappings of the 128-row query tile:
-//   prompt portions  rows = 128 consecutive tokens of one query head of one sequence
-//   decode           rows = the query heads that share one KV head, for a sequence's single new
-//                    token (rows past the group are ballast); the context is split over several
-//                    blocks, whose partial (reference maximum, sum, output) are merged by the block
-//                    that arrives last at the (sequence, KV head) counter
+// Two kernels over tiles of 128 consecutive tokens of a sequence:
+//   attention_tcgen05_pair_kernel  two query heads that share a KV head per block (an even number
+//                                  of query heads per KV head), probabilities kept in tensor memory
+//   attention_tcgen05_kernel       one query head per block, probabilities through shared memory
 //
-// Block = 6 warps: warp 0 lane 0 walks the block table and issues one 5-D TMA copy per page and
-// half of the head (the whole cache group's pool is ONE tensor map: dim, slot, KV head, page,
-// layer x {K, V}); warp 1 lane 0 issues the MMAs; warps 2-5 own one query row per thread: they
-// read the row's 128 scores from tensor memory, keep the running maximum and sum, write the
+// Common to both: warp 0 walks the block table and issues one 5-D TMA copy per page and half of the
+// head, one copy per lane (the whole cache group's pool is ONE tensor map: dim, slot, KV head, page,
+// layer x {K, V}); warp 1 lane 0 issues the MMAs; the softmax warps own one query row per thread:
+// they read the row's 128 scores from tensor memory, keep the running maximum and sum, write the
 // probabilities as the bf16 A operand of the second product and rescale the output only when the
 // maximum has grown by more than 2^8 (the accumulated values stay exact relative to a reference
 // maximum; the final division uses the same reference). Every mbarrier wait is bounded.
 //
-// Limits: head size 128, page size a multiple of 8 that divides 128, at most 128 query heads per KV
-// head in decode; anything else is refused (the mma.sync kernels of attention_mma.cu take it).
+// Limits: head size 128, page size a multiple of 8 that divides 128; anything else is refused (the
+// mma.sync kernels of attention_mma.cu take it). Decode steps use attention_mma.cu's split kernel:
+// two tcgen05 formulations of it (heads on the MMA rows, keys on the MMA rows) were measured at
+// 40 us against 28 us at batch 8 and 3.1 against 5.1 TB/s at batch 64 and are not kept.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
@@ -198,14 +197,11 @@ struct Args {
   int table_width;
   const int* cu_q;
   const int* ctx_len;
-  const int* tile_seq;      // prompt portions: the tile list; decode: null
+  const int* tile_seq;      // the tiles of 128 queries: sequence and first query of each
   const int* tile_q0;
   int q_heads, kv_heads, page_tokens, window;
   int layer2;               // 2 * layer: the K plane of this layer in the pool's last dimension
   float scale_log2;
-  int splits;               // decode only
-  float* partials;
-  unsigned* counters;
 };
 
 // The producer warp's loop. K and V tiles are requested independently, each as soon as its own
@@ -268,7 +264,6 @@ __device__ __forceinline__ void produce_kv(const CUtensorMap* kv_map, const Args
 
 constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * KV_STAGES) + 1024 + 512 + TABLE_CACHE * 4;   // Q, P, K and V stages, slack, barriers, table
 
-template <bool DECODE>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                          const Args args) {
@@ -295,33 +290,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // ---- what this block works on
-  int seq, head, kv_head, q_row, n_rows, p_first, p_last, tile_begin, tile_end, key_lo;
+  // heads run fastest and the tile list is walked backwards: within a sequence later tiles have
+  // more keys to visit, and the longest jobs should start first
   const int group = args.q_heads / args.kv_heads;
-  if (DECODE) {
-    seq = blockIdx.x; kv_head = blockIdx.y; head = kv_head * group;
-    const int ctx = args.ctx_len[seq];
-    p_first = p_last = ctx - 1;
-    key_lo = args.window > 0 ? max(0, p_last - args.window + 1) : 0;
-    const int first_tile = key_lo / KEYS, n_tiles = p_last / KEYS + 1 - first_tile;
-    const int per_split = (n_tiles + args.splits - 1) / args.splits;
-    tile_begin = first_tile + blockIdx.z * per_split;
-    tile_end = min(first_tile + n_tiles, tile_begin + per_split);
-    q_row = args.cu_q[seq] * args.q_heads + head;     // row of q viewed as [tokens * heads, dim]
-    n_rows = group;
-  } else {
-    // heads run fastest and the tile list is walked backwards: within a sequence later tiles have
-    // more keys to visit, and the longest jobs should start first
-    const int tile_index = gridDim.y - 1 - blockIdx.y;
-    seq = args.tile_seq[tile_index];
-    const int q0 = args.tile_q0[tile_index];
-    head = blockIdx.x; kv_head = head / group;
-    const int row0 = args.cu_q[seq], q_len = args.cu_q[seq + 1] - row0, ctx = args.ctx_len[seq];
-    n_rows = min(ROWS, q_len - q0);
-    p_first = ctx - q_len + q0; p_last = p_first + n_rows - 1;
-    key_lo = args.window > 0 ? max(0, p_first - args.window + 1) : 0;
-    tile_begin = key_lo / KEYS; tile_end = p_last / KEYS + 1;
-    q_row = row0 + q0;                                   // row of q viewed as [tokens, heads * dim]
-  }
+  const int tile_index = gridDim.y - 1 - blockIdx.y;
+  const int seq = args.tile_seq[tile_index], q0 = args.tile_q0[tile_index];
+  const int head = blockIdx.x, kv_head = head / group;
+  const int row0 = args.cu_q[seq], q_len = args.cu_q[seq + 1] - row0, ctx = args.ctx_len[seq];
+  const int n_rows = min(ROWS, q_len - q0);
+  const int p_first = ctx - q_len + q0, p_last = p_first + n_rows - 1;
+  const int key_lo = args.window > 0 ? max(0, p_first - args.window + 1) : 0;
+  const int tile_begin = key_lo / KEYS, tile_end = p_last / KEYS + 1;
+  const int q_row = row0 + q0;                             // row of q viewed as [tokens, heads * dim]
   const int n_tiles_mine = max(0, tile_end - tile_begin);
   const int* table = args.block_table + (size_t)seq * args.table_width;
 
@@ -355,7 +335,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       if (lane == 0) {
         mbar_expect_tx(q_full, TILE_BYTES);
         for (int half = 0; half < 2; ++half)
-          tma_load_2d(q_s + half * HALF_BYTES, &q_map, q_full, (DECODE ? 0 : head * DIM) + half * 64, q_row);
+          tma_load_2d(q_s + half * HALF_BYTES, &q_map, q_full, head * DIM + half * 64, q_row);
       }
       produce_kv<KV_STAGES>(&kv_map, args, k_s, v_s, k_full, k_empty, v_full, v_empty, page_cache, table, tile_begin,
                             n_tiles_mine, kv_head, flag, 1, lane);
@@ -407,7 +387,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     // ---------------- softmax and epilogue: one query row per thread
     const int quarter = warp & 3, row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int p_row = DECODE ? p_last : p_first + row;        // rows past n_rows are ballast
+    const int p_row = p_first + row;                          // rows past n_rows are ballast
     const float c = args.scale_log2;
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
@@ -506,22 +486,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     }
 
     // ---- the block's result: wait for the last second product, read the row, divide, store
-    float* my_partial = nullptr;
-    const int mstride = DIM + 2;
-    const unsigned tile_id = DECODE ? blockIdx.x * gridDim.y + blockIdx.y : 0;
-    if (DECODE && args.splits > 1)
-      my_partial = args.partials + ((size_t)tile_id * args.splits + blockIdx.z) * group * mstride;
     if (ok && n_tiles_mine > 0) {
       if (!mbar_wait(pv_done, (n_tiles_mine - 1) & 1)) { atomicCAS(&g_attn_error, 0, 8); flag[0] = 1; ok = false; }
       fence_after_sync();
     }
     if (ok) {
+      // tensor-memory loads are warp-wide: every lane reads its row, rows of the tile only are stored
       const bool valid = row < n_rows;
-      bf16* dst = nullptr;
-      if (valid) {
-        if (DECODE) dst = args.out + ((size_t)args.cu_q[seq] * args.q_heads + head + row) * DIM;
-        else dst = args.out + ((size_t)(q_row + row) * args.q_heads + head) * DIM;
-      }
+      bf16* dst = args.out + ((size_t)(q_row + (valid ? row : 0)) * args.q_heads + head) * DIM;
       const float inv = 1.0f / l_sum;
 #pragma unroll
       for (int ch = 0; ch < DIM / 16; ++ch) {
@@ -533,60 +505,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           for (int e = 0; e < 16; ++e) v[e] = 0.f;
         }
         if (!valid) continue;
-        if (my_partial) {
+        uint32_t w[8];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) my_partial[row * mstride + ch * 16 + e] = v[e];
-        } else {
-          uint32_t w[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * e] * inv, v[2 * e + 1] * inv);
-            w[e] = *reinterpret_cast<const uint32_t*>(&pair);
-          }
-          reinterpret_cast<uint4*>(dst + ch * 16)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          reinterpret_cast<uint4*>(dst + ch * 16)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        for (int e = 0; e < 8; ++e) {
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * e] * inv, v[2 * e + 1] * inv);
+          w[e] = *reinterpret_cast<const uint32_t*>(&pair);
         }
-      }
-      if (my_partial && valid) {     // the reference maximum in the units of the exponent, and the sum
-        my_partial[row * mstride + DIM] = (m_ref == -INFINITY) ? -INFINITY : m_ref * c;
-        my_partial[row * mstride + DIM + 1] = l_sum;
-      }
-    }
-    if (DECODE && args.splits > 1) {
-      // ---- the block that arrives last merges the splits in order
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) flag[1] = atomicAdd(&args.counters[tile_id], 1u) == (unsigned)args.splits - 1 ? 1u : 0u;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (flag[1]) {
-        __threadfence();
-        const float* all = args.partials + (size_t)tile_id * args.splits * group * mstride;
-        float* factor = reinterpret_cast<float*>(q_s);          // [splits][group], the query tile is done with
-        float* l_total = factor + (size_t)args.splits * group;
-        const int t = threadIdx.x - 64;
-        for (int i = t; i < args.splits * group; i += 128) factor[i] = all[(size_t)i * mstride + DIM];   // maxima first
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int r = t; r < group; r += 128) {
-          float m_all = -INFINITY;
-          for (int s2 = 0; s2 < args.splits; ++s2) m_all = fmaxf(m_all, factor[s2 * group + r]);
-          const float base = m_all == -INFINITY ? 0.f : m_all;
-          float l_all = 0.f;
-          for (int s2 = 0; s2 < args.splits; ++s2) {
-            const float f = fast_exp2(factor[s2 * group + r] - base);
-            l_all += all[((size_t)s2 * group + r) * mstride + DIM + 1] * f;
-            factor[s2 * group + r] = f;
-          }
-          l_total[r] = l_all;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int i = t; i < group * DIM; i += 128) {
-          const int r = i / DIM, col = i % DIM;
-          float acc = 0.f;
-#pragma unroll 8
-          for (int s2 = 0; s2 < args.splits; ++s2) acc += all[((size_t)s2 * group + r) * mstride + col] * factor[s2 * group + r];
-          args.out[((size_t)args.cu_q[seq] * args.q_heads + head + r) * DIM + col] = __float2bfloat16_rn(acc / l_total[r]);
-        }
-        if (threadIdx.x == 64) args.counters[tile_id] = 0;
+        reinterpret_cast<uint4*>(dst + ch * 16)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(dst + ch * 16)[1] = make_uint4(w[4], w[5], w[6], w[7]);
       }
     }
   }
@@ -877,316 +803,6 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
   }
 }
 
-// ------------------------------------------------------------------------------- decode, keys on the rows
-// The decode kernel proper. With one new token per sequence there are only `group` query rows, so
-// the products are turned around: S^T = K Q^T puts the 128 keys of a tile on the rows of the MMA
-// (one key per softmax thread, `group` scores each instead of 128) and the group's heads on its 16
-// columns; O^T = V^T P^T puts the head's 128 dims on the rows. The running maximum is the same for
-// all threads (a warp shuffle and one exchange through shared memory per tile), the sums stay per
-// thread until the end. Splits, partials and their merge are those of the other decode kernels.
-constexpr int HEAD_COLS = 16;                          // columns of the turned products (group <= 16)
-constexpr int QT_HALF = HEAD_COLS * 128;               // one 64-wide half of a 16-row K-major operand: 2 KiB
-constexpr int T_STAGES = 3;
-constexpr int T_SMEM = 2 * T_STAGES * TILE_BYTES + 4 * QT_HALF + 1024 + 1024 + TABLE_CACHE * 4;   // K, V stages, Q^T, P^T, slack, barriers + exchange, table
-
-constexpr uint32_t instr_desc_t(bool a_mn) {           // M = 128, N = 16
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((uint32_t)(HEAD_COLS >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-
-__global__ void __launch_bounds__(THREADS, 1)
-attention_tcgen05_decode_t_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
-                                  const Args args) {
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
-  uint8_t* k_s = smem;                                   // [T_STAGES][TILE_BYTES]
-  uint8_t* v_s = k_s + T_STAGES * TILE_BYTES;
-  uint8_t* q_s = v_s + T_STAGES * TILE_BYTES;            // Q as the 16-row B operand, two halves
-  uint8_t* p_s = q_s + 2 * QT_HALF;                      // P^T as the 16-row B operand, two halves
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * QT_HALF);
-  uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;        // [3]
-  uint64_t* k_empty = bars + 4;
-  uint64_t* v_full = bars + 7;
-  uint64_t* v_empty = bars + 10;
-  uint64_t* s_full = bars + 13;       // [2]
-  uint64_t* s_empty = bars + 15;      // [2]
-  uint64_t* p_full = bars + 17;
-  uint64_t* pv_done = bars + 18;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
-  volatile uint32_t* flag = tmem_slot + 1;
-  float* exchange = reinterpret_cast<float*>(tmem_slot + 4);   // [4 warps][16] maxima, then [4][16] sums
-  int* page_cache = reinterpret_cast<int*>(bars) + 256;        // after the 1024 bytes of barriers and exchange
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int group = args.q_heads / args.kv_heads;
-  const int seq = blockIdx.x, kv_head = blockIdx.y, head = kv_head * group;
-  const int ctx = args.ctx_len[seq], p_last = ctx - 1;
-  const int key_lo = args.window > 0 ? max(0, p_last - args.window + 1) : 0;
-  const int first_tile = key_lo / KEYS, n_tiles = p_last / KEYS + 1 - first_tile;
-  const int per_split = (n_tiles + args.splits - 1) / args.splits;
-  const int tile_begin = first_tile + blockIdx.z * per_split;
-  const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
-  const int n_mine = max(0, tile_end - tile_begin);
-  const int q_row = args.cu_q[seq] * args.q_heads + head;
-  const int* table = args.block_table + (size_t)seq * args.table_width;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < T_STAGES; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-    }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
-    flag[0] = 0; flag[1] = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    fence_async_smem();
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, 64);
-  fence_before_sync();
-  __syncthreads();
-  fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;            // two score buffers of 16 columns
-  const uint32_t tmem_o = tmem_base + 32;       // O^T: 128 lanes (dims) x 16 columns (heads)
-  pdl_launch_dependents();
-  pdl_wait();
-
-  if (warp == 0) {
-    const int pages_per_tile = KEYS / args.page_tokens;
-    if (n_mine > 0) cache_pages(page_cache, table, args.table_width, tile_begin * pages_per_tile, n_mine * pages_per_tile, lane);
-    if (n_mine > 0) {
-      if (lane == 0) {
-        mbar_expect_tx(q_full, 2 * QT_HALF);
-        for (int half = 0; half < 2; ++half) tma_load_2d(q_s + half * QT_HALF, &q_map, q_full, half * 64, q_row);
-      }
-      produce_kv<T_STAGES>(&kv_map, args, k_s, v_s, k_full, k_empty, v_full, v_empty, page_cache, table, tile_begin, n_mine,
-                           kv_head, flag, 11, lane);
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && n_mine > 0) {
-      constexpr uint32_t idesc_s = instr_desc_t(false), idesc_o = instr_desc_t(true);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok) { atomicCAS(&g_attn_error, 0, 12); flag[0] = 1; }
-      auto issue_s = [&](int i) {
-        const int stage = i % T_STAGES, buf = i & 1;
-        if (!mbar_wait(&k_full[stage], (i / T_STAGES) & 1) || !mbar_wait(&s_empty[buf], ((i >> 1) & 1) ^ 1)) {
-          atomicCAS(&g_attn_error, 0, 13); flag[0] = 1; return false;
-        }
-        fence_after_sync();
-        const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s + stage * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < DIM / 16; ++ks)      // A = K rows (keys), B = Q rows (heads), both K-major over dims
-          umma_bf16(tmem_s + buf * HEAD_COLS, desc_k_major(k_addr + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
-                    desc_k_major(q_addr + (ks >> 2) * QT_HALF + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(&s_full[buf]);
-        umma_commit(&k_empty[stage]);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int i = 0; i < n_mine && ok; ++i) {
-        if (i + 1 < n_mine) ok = issue_s(i + 1);
-        if (!ok) break;
-        const int stage = i % T_STAGES;
-        if (!mbar_wait(p_full, i & 1) || !mbar_wait(&v_full[stage], (i / T_STAGES) & 1)) {
-          atomicCAS(&g_attn_error, 0, 14); flag[0] = 1; break;
-        }
-        fence_after_sync();
-        const uint32_t p_addr = smem_u32(p_s), v_addr = smem_u32(v_s + stage * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < KEYS / 16; ++ks)     // A = V read with its dims along the rows, B = P^T rows (heads) over keys
-          umma_bf16(tmem_o, desc_mn_major(v_addr + ks * 16 * 128), desc_k_major(p_addr + (ks >> 2) * QT_HALF + (ks & 3) * 32),
-                    idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(pv_done);
-        umma_commit(&v_empty[stage]);
-      }
-    }
-  } else {
-    // ---------------- softmax: one key per thread
-    const int quarter = warp & 3, j = quarter * 32 + lane;     // key within the tile; later: the dim of the output
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const float c = args.scale_log2;
-    float m_ref[HEAD_COLS], l_part[HEAD_COLS];
-#pragma unroll
-    for (int h = 0; h < HEAD_COLS; ++h) { m_ref[h] = -INFINITY; l_part[h] = 0.f; }
-    bool ok = true;
-    for (int i = 0; i < n_mine && ok; ++i) {
-      const int tile = tile_begin + i, buf = i & 1, stage = i % T_STAGES;
-      const int key = tile * KEYS + j;
-      if (!mbar_wait(&s_full[buf], (i >> 1) & 1)) { atomicCAS(&g_attn_error, 0, 15); flag[0] = 1; ok = false; break; }
-      fence_after_sync();
-      float s[HEAD_COLS];
-      tmem_ld16(tmem_s + buf * HEAD_COLS + lane_addr, s);
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[buf]);
-      const bool seen = key <= p_last && key >= key_lo;
-      // the tile's maximum per head: over the warp by shuffles, over the four warps through shared memory
-      float tile_max[HEAD_COLS];
-#pragma unroll
-      for (int h = 0; h < HEAD_COLS; ++h) {
-        float v = (h < group && seen) ? s[h] : -INFINITY;
-        s[h] = v;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        tile_max[h] = v;
-      }
-#pragma unroll
-      for (int h = 0; h < HEAD_COLS; ++h)       // after the butterfly every lane holds every maximum
-        if (lane == h) exchange[quarter * HEAD_COLS + h] = tile_max[h];
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      bool any_grow = false;
-      float factor[HEAD_COLS];
-#pragma unroll
-      for (int h = 0; h < HEAD_COLS; ++h) {
-        const float m_tile = fmaxf(fmaxf(exchange[h], exchange[HEAD_COLS + h]), fmaxf(exchange[2 * HEAD_COLS + h], exchange[3 * HEAD_COLS + h]));
-        const bool grow = (m_tile - m_ref[h]) * c > RESCALE_THRESHOLD || (m_ref[h] == -INFINITY && m_tile > -INFINITY);
-        const float m_new = grow ? m_tile : m_ref[h];
-        factor[h] = (m_ref[h] == -INFINITY) ? 0.f : fast_exp2((m_ref[h] - m_new) * c);
-        any_grow |= grow;
-        m_ref[h] = m_new;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");      // the exchange buffer may be written again
-      uint16_t pbits[HEAD_COLS];
-#pragma unroll
-      for (int h = 0; h < HEAD_COLS; ++h) {
-        const float base = (m_ref[h] == -INFINITY) ? 0.f : m_ref[h];
-        const float pv = fast_exp2((s[h] - base) * c);         // 0 for keys that are not seen and for ballast heads
-        l_part[h] = l_part[h] * factor[h] + pv;
-        const bf16 b = __float2bfloat16_rn(pv);
-        pbits[h] = *reinterpret_cast<const uint16_t*>(&b);
-      }
-      if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) { atomicCAS(&g_attn_error, 0, 16); flag[0] = 1; ok = false; break; }
-      fence_after_sync();
-      if (any_grow && i > 0) {       // O^T: this thread's lane is a dim, the columns are heads
-        float v[16];
-        tmem_ld16(tmem_o + lane_addr, v);
-#pragma unroll
-        for (int h = 0; h < HEAD_COLS; ++h) v[h] *= factor[h];
-        tmem_st16(tmem_o + lane_addr, v);
-      }
-      // P^T[h][key]: row h of a 16-row K-major operand, 2 bytes at key j
-      {
-        const int half = j >> 6, chunk = (j & 63) >> 3, within = (j & 7) * 2;
-#pragma unroll
-        for (int h = 0; h < HEAD_COLS; ++h)
-          *reinterpret_cast<uint16_t*>(p_s + half * QT_HALF + h * 128 + ((chunk ^ (h & 7)) << 4) + within) = pbits[h];
-      }
-      const int limit = p_last + 1, key0 = tile * KEYS;
-      if (key0 + KEYS > limit || key0 < key_lo) {
-        if (!mbar_wait(&v_full[stage], (i / T_STAGES) & 1)) { atomicCAS(&g_attn_error, 0, 17); flag[0] = 1; ok = false; break; }
-        if (!seen) {                  // this thread's key is outside the context: its value row must not count
-          uint8_t* vrow = v_s + stage * TILE_BYTES + j * 128;
-#pragma unroll
-          for (int chunk = 0; chunk < 8; ++chunk) {
-            *reinterpret_cast<uint4*>(vrow + chunk * 16) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(vrow + HALF_BYTES + chunk * 16) = make_uint4(0, 0, 0, 0);
-          }
-        }
-      }
-      fence_async_smem();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-    }
-
-    // ---- sums over all keys (threads), then this thread's dim of every head
-    float l_sum[HEAD_COLS];
-#pragma unroll
-    for (int h = 0; h < HEAD_COLS; ++h) {
-      float v = l_part[h];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      l_sum[h] = v;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-    for (int h = 0; h < HEAD_COLS; ++h)
-      if (lane == h) exchange[quarter * HEAD_COLS + h] = l_sum[h];
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-    for (int h = 0; h < HEAD_COLS; ++h)
-      l_sum[h] = (exchange[h] + exchange[HEAD_COLS + h]) + (exchange[2 * HEAD_COLS + h] + exchange[3 * HEAD_COLS + h]);
-    if (ok && n_mine > 0) {
-      if (!mbar_wait(pv_done, (n_mine - 1) & 1)) { atomicCAS(&g_attn_error, 0, 18); flag[0] = 1; ok = false; }
-      fence_after_sync();
-    }
-    const int mstride = DIM + 2;
-    const unsigned tile_id = blockIdx.x * gridDim.y + blockIdx.y;
-    float* my_partial = args.splits > 1 ? args.partials + ((size_t)tile_id * args.splits + blockIdx.z) * group * mstride : nullptr;
-    if (ok) {
-      float v[16];
-      if (n_mine > 0) {
-        tmem_ld16(tmem_o + lane_addr, v);
-      } else {
-#pragma unroll
-        for (int h = 0; h < 16; ++h) v[h] = 0.f;
-      }
-      bf16* dst = args.out + ((size_t)args.cu_q[seq] * args.q_heads + head) * DIM + j;
-#pragma unroll
-      for (int h = 0; h < HEAD_COLS; ++h) {
-        if (h >= group) continue;
-        if (my_partial) {
-          my_partial[h * mstride + j] = v[h];
-          if (j == 0) {
-            my_partial[h * mstride + DIM] = (m_ref[h] == -INFINITY) ? -INFINITY : m_ref[h] * c;
-            my_partial[h * mstride + DIM + 1] = l_sum[h];
-          }
-        } else {
-          dst[(size_t)h * DIM] = __float2bfloat16_rn(v[h] / l_sum[h]);
-        }
-      }
-    }
-    if (args.splits > 1) {
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) flag[1] = atomicAdd(&args.counters[tile_id], 1u) == (unsigned)args.splits - 1 ? 1u : 0u;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (flag[1]) {
-        __threadfence();
-        const float* all = args.partials + (size_t)tile_id * args.splits * group * mstride;
-        float* factor = reinterpret_cast<float*>(k_s);           // [splits][group]; the tiles are done with
-        float* l_total = factor + (size_t)args.splits * group;
-        const int t = threadIdx.x - 64;
-        for (int i = t; i < args.splits * group; i += 128) factor[i] = all[(size_t)i * mstride + DIM];
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int r = t; r < group; r += 128) {
-          float m_all = -INFINITY;
-          for (int s2 = 0; s2 < args.splits; ++s2) m_all = fmaxf(m_all, factor[s2 * group + r]);
-          const float base = m_all == -INFINITY ? 0.f : m_all;
-          float l_all = 0.f;
-          for (int s2 = 0; s2 < args.splits; ++s2) {
-            const float f = fast_exp2(factor[s2 * group + r] - base);
-            l_all += all[((size_t)s2 * group + r) * mstride + DIM + 1] * f;
-            factor[s2 * group + r] = f;
-          }
-          l_total[r] = l_all;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int i = t; i < group * DIM; i += 128) {
-          const int r = i / DIM, col = i % DIM;
-          float acc = 0.f;
-#pragma unroll 8
-          for (int s2 = 0; s2 < args.splits; ++s2) acc += all[((size_t)s2 * group + r) * mstride + col] * factor[s2 * group + r];
-          args.out[((size_t)args.cu_q[seq] * args.q_heads + head + r) * DIM + col] = __float2bfloat16_rn(acc / l_total[r]);
-        }
-        if (threadIdx.x == 64) args.counters[tile_id] = 0;
-      }
-    }
-  }
-
-  fence_before_sync();
-  __syncthreads();
-  if (flag[0]) {
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    fence_after_sync();
-    tmem_dealloc(tmem_base, 64);
-  }
-}
-
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
     void* p = nullptr;
@@ -1202,20 +818,18 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 void configure_once() {
   static bool done = false;
   if (done) return;
-  cudaFuncSetAttribute(attention_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  cudaFuncSetAttribute(attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  cudaFuncSetAttribute(attention_tcgen05_decode_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+  cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   cudaFuncSetAttribute(attention_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
   done = true;
 }
 
 // q as a 2-D bf16 matrix [rows, cols] with rows `stride` elements apart: box 64 columns x 128 rows
-bool make_q_map(CUtensorMap* map, const void* q, long rows, long cols, long stride, int box_rows = ROWS) {
+bool make_q_map(CUtensorMap* map, const void* q, long rows, long cols, long stride) {
   auto encode = encode_fn();
   if (!encode) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)stride * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {64, (cuuint32_t)ROWS};
   cuuint32_t elem[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, elem,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1271,45 +885,13 @@ LB_EXPORT int lb_attention_tcgen05_prefill(const void* q, long q_rows, const voi
   if (!make_q_map(&q_map, q, q_rows, (long)q_heads * dim, (long)q_heads * dim)) return LB_ERR_ALIGN;
   memcpy(&kv_map, pool_map, sizeof(kv_map));
   Args args{(bf16*)out, block_table, table_width, cu_q, ctx_len, tile_seq, tile_q0, q_heads, kv_heads, page_tokens, window,
-            2 * layer, scale * 1.4426950408889634f, 1, nullptr, nullptr};
+            2 * layer, scale * 1.4426950408889634f};
   int code;
   if ((q_heads / kv_heads) % 2 == 0)    // two heads of a KV head per block
     code = lb_launch(attention_tcgen05_pair_kernel, dim3(q_heads / 2, n_tiles), dim3(PAIR_THREADS), (size_t)PAIR_SMEM, stream,
                      q_map, kv_map, args);
   else
-    code = lb_launch(attention_tcgen05_kernel<false>, dim3(q_heads, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES, stream,
+    code = lb_launch(attention_tcgen05_kernel, dim3(q_heads, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES, stream,
                      q_map, kv_map, args);
-  return code ? code : lb_last_error();
-}
-
-// Sequences with one new token each, in order; grid (sequences, KV heads, splits).
-LB_EXPORT int lb_attention_tcgen05_decode(const void* q, long q_rows, const void* pool_map, int layer, void* out,
-                                          const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
-                                          int n_seqs, int q_heads, int kv_heads, int dim, int page_tokens, float scale,
-                                          int window, int splits, float* partials, long partial_floats, unsigned* counters,
-                                          int n_counters, cudaStream_t stream) {
-  if (n_seqs <= 0) return 0;
-  if (!lb_attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens) || kv_heads > 65535 || splits < 1 || splits > 65535)
-    return LB_ERR_SIZE;
-  const int group = q_heads / kv_heads;
-  if (splits > 1 && (!partials || !counters || (long)n_seqs * q_heads * splits * (dim + 2) > partial_floats ||
-                     (long)n_seqs * kv_heads > n_counters || (size_t)(splits + 1) * group * sizeof(float) > TILE_BYTES))
-    return LB_ERR_SIZE;
-  if ((uintptr_t)q % 16) return LB_ERR_ALIGN;
-  configure_once();
-  CUtensorMap q_map, kv_map;
-  memcpy(&kv_map, pool_map, sizeof(kv_map));
-  Args args{(bf16*)out, block_table, table_width, cu_q, ctx_len, nullptr, nullptr, q_heads, kv_heads, page_tokens, window,
-            2 * layer, scale * 1.4426950408889634f, splits, partials, counters};
-  int code;
-  if (group <= HEAD_COLS) {       // keys on the rows: the kernel made for decode
-    if (!make_q_map(&q_map, q, q_rows * q_heads, dim, dim, HEAD_COLS)) return LB_ERR_ALIGN;
-    code = lb_launch(attention_tcgen05_decode_t_kernel, dim3(n_seqs, kv_heads, splits), dim3(THREADS), (size_t)T_SMEM, stream,
-                     q_map, kv_map, args);
-  } else {                        // more than 16 query heads per KV head: heads on the rows
-    if (!make_q_map(&q_map, q, q_rows * q_heads, dim, dim)) return LB_ERR_ALIGN;
-    code = lb_launch(attention_tcgen05_kernel<true>, dim3(n_seqs, kv_heads, splits), dim3(THREADS), (size_t)SMEM_BYTES, stream,
-                     q_map, kv_map, args);
-  }
   return code ? code : lb_last_error();
 }

@@ -489,24 +489,6 @@ def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, t
     return out
 
 
-def attention_tcgen05_decode(q, pool, layer, out, block_table, cu_q, ctx_len, n_seqs, q_heads, kv_heads, dim,
-                             page_tokens, scale, window=0, splits=1):
-    """One new token per sequence on tcgen05, the context split `splits` ways."""
-    for name, t in (("q", q), ("out", out)):
-        _need(t, torch.bfloat16, name)
-    for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len)):
-        _need(t, torch.int32, name)
-    partials, counters = attention_scratch(q.device)
-    fn = _fn("attention_tcgen05", "lb_attention_tcgen05_decode",
-             [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 5 +
-             [c_float, c_int, c_int, c_void_p, c_long, c_void_p, c_int, c_void_p])
-    _check(fn(_ptr(q), q.shape[0], ctypes.addressof(_pool_map(pool)), int(layer), _ptr(out), _ptr(block_table),
-              block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale),
-              int(window), int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), _stream()),
-           "attention_tcgen05_decode")
-    return out
-
-
 def attention_bf16_tile_sizes() -> tuple[int, ...]:
     return (attention_mma_block_queries(), TCGEN05_TILE)
 

@@ -488,7 +488,7 @@ def test_gemm_tcgen05_swiglu_epilogue(m, inter, k):
         o.gemm_tcgen05(a, w[:2 * inter - 64], torch.empty(m, inter - 32, device="cuda", dtype=torch.bfloat16), epilogue="swiglu")
 
 
-def run_tc_attention(lengths, q_lens, q_heads, kv_heads, page, window=0, seed=0, decode=False, splits=1, layers=3, layer=1):
+def run_tc_attention(lengths, q_lens, q_heads, kv_heads, page, window=0, seed=0, layers=3, layer=1):
     """The tcgen05 kernels against the plain attention: the pool has several layers and both planes,
     as the cache manager lays it out, and only plane (layer, K / V) holds the data."""
     o = ops()
@@ -504,15 +504,11 @@ def run_tc_attention(lengths, q_lens, q_heads, kv_heads, page, window=0, seed=0,
     ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
     out = torch.full_like(q, float("nan"))
     scale = 1.0 / math.sqrt(dim)
-    if decode:
-        o.attention_tcgen05_decode(q, pool, layer, out, table, cu, ctx, len(lengths), q_heads, kv_heads, dim, page, scale,
-                                   window, splits)
-    else:
-        tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, 128)]
-        tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
-        tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
-        o.attention_tcgen05_prefill(q, pool, layer, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads,
-                                    dim, page, scale, window)
+    tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, 128)]
+    tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+    tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+    o.attention_tcgen05_prefill(q, pool, layer, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads,
+                                dim, page, scale, window)
     assert o.attention_tcgen05_status() == 0
     expected = []
     for s, n in enumerate(lengths):
@@ -536,16 +532,6 @@ def test_attention_tcgen05_prefill(q_heads, kv_heads, page):
 def test_attention_tcgen05_prefill_window(window):
     got, expected = run_tc_attention([270, 440, 33], [270, 3, 1], 4, 2, 16, window=window)
     close(got, expected, torch.bfloat16)
-
-
-@pytest.mark.parametrize("splits", [1, 2, 5])
-@pytest.mark.parametrize("q_heads, kv_heads, page", [(4, 1, 16), (32, 8, 16), (16, 1, 8), (6, 6, 32)])
-def test_attention_tcgen05_decode(q_heads, kv_heads, page, splits):
-    lengths = [1, 2, page, page + 1, 127, 128, 129, 255, 256, 257, 700, 1000]
-    for _ in range(2):
-        got, expected = run_tc_attention(lengths, [1] * len(lengths), q_heads, kv_heads, page, decode=True, splits=splits)
-        assert not torch.isnan(got).any()
-        close(got, expected, torch.bfloat16)
 
 
 @pytest.mark.parametrize("heads", [1, 2])
