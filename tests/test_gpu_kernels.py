@@ -3,6 +3,7 @@ other than the engine's own tiny models: widths that are no power of two, head s
 16, any number of heads and groups, pages of several sizes."""
 
 import math
+import os
 
 import numpy as np
 import pytest
@@ -460,7 +461,8 @@ def test_fused_qkv_projection_equals_product_then_head_kernel(q_heads, kv_heads,
         taken = o.gemm_qkv_heads(h, w, q2, k2, v2, q_w, k_w, table, slots, q_heads, kv_heads, dim, page, 1e-6)
     assert o.gemm_status() == 0
     if not taken:
-        assert hidden // 64 < 8 or rows // 128 >= 148      # too few K blocks to split, or nothing to split for
+        # too few K blocks to split, nothing to split for, or clusters switched off for the run
+        assert hidden // 64 < 8 or rows // 128 >= 148 or os.environ.get("LAYOVER_B200_CLUSTER_REDUCE") == "0"
         return
     assert torch.equal(q1, q2)
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
