@@ -148,6 +148,18 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The maximum of a row's scores over four chains that do not wait for one another (one chain of 128
+// dependent comparisons costs more than the exponentials that follow).
+template <int N>
+__device__ __forceinline__ float row_max(const float (&s)[N]) {
+  float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int e = 0; e < N; e += 4) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) m[k] = fmaxf(m[k], s[e + k]);
+  }
+  return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -419,8 +431,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           if (!seen) s[e] = -INFINITY;
         }
       }
-#pragma unroll
-      for (int e = 0; e < KEYS; ++e) tile_max = fmaxf(tile_max, s[e]);
+      tile_max = row_max(s);
       // The reference maximum only moves when the true one has outgrown it by 2^8: the accumulated
       // output then needs no rescaling for most tiles. A warp rescales together (tensor-memory
       // loads and stores are warp-wide), every lane by its own factor.
@@ -433,15 +444,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * c);
       const float neg_base = (m_new == -INFINITY) ? 0.f : -m_new * c;
       uint32_t w[KEYS / 2];
-      float tile_sum = 0.f;
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};           // four chains of additions side by side
 #pragma unroll
       for (int e = 0; e < KEYS / 2; ++e) {
         const float a = fast_exp2(fmaf(s[2 * e], c, neg_base));
         const float b = fast_exp2(fmaf(s[2 * e + 1], c, neg_base));
-        tile_sum += a + b;
+        part_sum[e & 3] += a + b;
         const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
         w[e] = *reinterpret_cast<const uint32_t*>(&pair);
       }
+      const float tile_sum = (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
       l_sum = l_sum * factor + tile_sum;
       m_ref = m_new;
       if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) { atomicCAS(&g_attn_error, 0, 6); flag[0] = 1; ok = false; break; }
@@ -697,16 +709,14 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
           if (!seen) s[e] = -INFINITY;
         }
       }
-      float tile_max = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < KEYS; ++e) tile_max = fmaxf(tile_max, s[e]);
+      const float tile_max = row_max(s);
       // the reference maximum only moves when the true one has outgrown it by 2^8 (see the kernel above)
       const bool grow = (tile_max - m_ref) * c > RESCALE_THRESHOLD || (m_ref == -INFINITY && tile_max > -INFINITY);
       const bool any_grow = __any_sync(0xffffffffu, grow);
       const float m_new = grow ? tile_max : m_ref;
       const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * c);
       const float neg_base = (m_new == -INFINITY) ? 0.f : -m_new * c;
-      float tile_sum = 0.f;
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};           // four chains of additions side by side
       // exponentials, 32 scores at a time: 16 columns of packed probabilities over the row's own scores
 #pragma unroll
       for (int ch = 0; ch < KEYS / 32; ++ch) {
@@ -715,12 +725,13 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
         for (int e = 0; e < 16; ++e) {
           const float a = fast_exp2(fmaf(s[ch * 32 + 2 * e], c, neg_base));
           const float b = fast_exp2(fmaf(s[ch * 32 + 2 * e + 1], c, neg_base));
-          tile_sum += a + b;
+          part_sum[e & 3] += a + b;
           const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
           w[e] = *reinterpret_cast<const uint32_t*>(&pair);
         }
         tmem_st16_nowait(my_s + ch * 16, w);
       }
+      const float tile_sum = (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
       l_sum = l_sum * factor + tile_sum;
       m_ref = m_new;
       if (any_grow && i > 0) {
