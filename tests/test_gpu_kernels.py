@@ -536,6 +536,55 @@ def test_attention_tcgen05_prefill_window(window):
     close(got, expected, torch.bfloat16)
 
 
+def tail_attention(q_tail, k, v, group):
+    """Causal attention for the last rows of a sequence only (32-bit, on the CPU): q_tail [n, heads, dim]
+    are the queries of the last n positions of keys k, v [len, kv_heads, dim]."""
+    n, length = q_tail.shape[0], k.shape[0]
+    kf = k.float().repeat_interleave(group, dim=1)
+    vf = v.float().repeat_interleave(group, dim=1)
+    scores = torch.einsum("qhd,khd->hqk", q_tail.float(), kf) / math.sqrt(q_tail.shape[-1])
+    position = torch.arange(length - n, length)[:, None]
+    scores = scores.masked_fill(torch.arange(length)[None, :] > position, float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), vf)
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "prefill", "decode", "decode16"])
+def test_attention_over_long_contexts(kernel):
+    """Contexts of some 20,000 keys: block tables wider than the slice that a block keeps in shared
+    memory (1,024 pages), many tiles per block, and for decode many splits."""
+    o = ops()
+    dim, page, q_heads, kv_heads = 128, 16, 4, 1
+    lengths = [20000, 17013]
+    q_lens = [1, 1] if kernel.startswith("decode") else [200, 130]
+    k_pool, v_pool, table, ks, vs = paged_setup(torch.bfloat16, lengths, kv_heads, dim, page, seed=3)
+    gen = torch.Generator().manual_seed(4)
+    qs = [torch.randn(n, q_heads, dim, generator=gen).to(torch.bfloat16) for n in q_lens]
+    q = torch.cat(qs).reshape(-1, q_heads * dim).cuda()
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    scale = 1.0 / math.sqrt(dim)
+    if kernel.startswith("decode"):
+        splits = 16 if kernel == "decode16" else o.decode_splits(2, q_heads, kv_heads, dim, max(lengths), 148)
+        o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, ctx, None, 2, q_heads, kv_heads, dim, page, scale, 0, splits)
+    else:
+        size = 128 if kernel == "tcgen05" else o.attention_mma_block_queries()
+        tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, size)]
+        tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+        tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+        if kernel == "tcgen05":
+            pool = torch.stack((k_pool, v_pool))[None].contiguous()
+            o.attention_tcgen05_prefill(q, pool, 0, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads,
+                                        dim, page, scale, 0)
+            assert o.attention_tcgen05_status() == 0
+        else:
+            o.attention_prefill_bf16(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads,
+                                     kv_heads, dim, page, scale, 0)
+    expected = torch.cat([tail_attention(qs[s], ks[s], vs[s], q_heads // kv_heads) for s in range(2)])
+    assert not torch.isnan(out).any()
+    close(out.cpu().view(-1, q_heads, dim), expected, torch.bfloat16)
+
+
 @pytest.mark.parametrize("heads", [1, 2])
 def test_attention_tcgen05_scores_far_apart_force_rescaling(heads):
     """Keys whose scores grow along the sequence make the running maximum jump by far more than the
