@@ -1006,19 +1006,21 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
     if (splits < 1) splits = 1;
   }
   dim3 grid(tiles, (pb.rows_b + BN - 1) / BN, splits);
-  if (EPI == 0 && BN <= 32 && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && lb_cluster_reduce_enabled()) {
-    // the K ranges of a tile as one cluster: partial sums travel through distributed shared memory
-    auto cluster_kernel = gemm_fewtoken_kernel<BN, OutT, EPI, true>;
-    static bool cluster_configured = false;
-    if (!cluster_configured) {
-      if (cudaFuncSetAttribute(cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_CLUSTER) != cudaSuccess)
-        return lb_last_error();
-      cluster_configured = true;
+  if constexpr (EPI == 0 && BN <= 32) {
+    if (splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && lb_cluster_reduce_enabled()) {
+      // the K ranges of a tile as one cluster: partial sums travel through distributed shared memory
+      auto cluster_kernel = gemm_fewtoken_kernel<BN, OutT, EPI, true>;
+      static bool cluster_configured = false;
+      if (!cluster_configured) {
+        if (cudaFuncSetAttribute(cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_CLUSTER) != cudaSuccess)
+          return lb_last_error();
+        cluster_configured = true;
+      }
+      const int code = lb_launch_cluster(cluster_kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream,
+                                         (unsigned)splits, map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, pb.K,
+                                         splits, (float*)nullptr, (unsigned*)nullptr, HeadsEpilogue{});
+      return code ? code : lb_last_error();
     }
-    const int code = lb_launch_cluster(cluster_kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream,
-                                       (unsigned)splits, map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, pb.K, splits,
-                                       (float*)nullptr, (unsigned*)nullptr, HeadsEpilogue{});
-    return code ? code : lb_last_error();
   }
   const int code = lb_launch(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM, stream, map_a, map_b, (OutT*)C, ldc,
                              pb.rows_a, pb.rows_b, pb.K, splits, splits > 1 ? pb.scratch : (float*)nullptr, pb.counters,
