@@ -381,3 +381,137 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
     finally:
         unregister("mixer", "running_mean")
         unregister_architecture("ToyMeanForCausalLM")
+
+
+def test_a_toy_position_encoding_and_a_toy_routed_feed_forward_run_in_the_same_blocks(tmp_path):
+    """Two more parts defined here, not in the package, beside the package's attention and norms: a
+    rotary encoding over positions divided by a factor, applied as a step of its own (it offers no
+    table for the fused kernel), and a feed-forward that routes every token to one of three gated
+    MLPs. Registered, built from a model folder, stepped whole, in portions and token by token."""
+    from layover_b200.config import register_architecture, unregister_architecture
+    from layover_b200.models import ModelSpec, LayerSpec
+    from layover_b200.parts import Part, PartSpec, register_feed_forward, register_position, unregister
+    from layover_b200.weights import TensorSpec
+    from plain_qwen3 import plain_apply_rope, plain_attention, plain_linear, plain_rope_tables
+
+    class ScaledRotary(Part):
+        def __init__(self, params, prefix):
+            super().__init__(params, prefix)
+            self.dim, self.theta, self.factor = params["dim"], params["theta"], params["factor"]
+
+        def tables(self, batch):
+            return None                                   # not something the fused kernel can apply
+
+        def apply(self, q, k, positions):
+            inv = 1.0 / (self.theta ** (torch.arange(0, self.dim, 2, dtype=torch.float32, device=q.device) / self.dim))
+            angle = (positions.float() / self.factor)[:, None] * inv[None, :]
+            cos, sin = torch.cat((angle, angle), -1).cos()[:, None, :], torch.cat((angle, angle), -1).sin()[:, None, :]
+            for x in (q, k):
+                if x is not None:
+                    half = self.dim // 2
+                    rotated = torch.cat((-x[..., half:], x[..., :half]), -1)
+                    x.copy_(x * cos + rotated * sin)
+
+    class Routed(Part):
+        def __init__(self, params, prefix):
+            super().__init__(params, prefix)
+            self.hidden, self.inter, self.experts = params["hidden"], params["inter"], params["experts"]
+
+        def names(self, e):
+            return [f"{self.prefix}mlp.experts.{e}.{n}.weight" for n in ("gate", "up", "down")]
+
+        def tensor_specs(self):
+            specs = [TensorSpec(self.prefix + "mlp.router.weight", (self.experts, self.hidden), kind="keep32")]
+            for e in range(self.experts):
+                g, u, d = self.names(e)
+                specs += [TensorSpec(g, (self.inter, self.hidden)), TensorSpec(u, (self.inter, self.hidden)),
+                          TensorSpec(d, (self.hidden, self.inter))]
+            return specs
+
+        def bind(self, tensors, runtime):
+            super().bind(tensors, runtime)
+            self.router = tensors[self.prefix + "mlp.router.weight"]
+            self.weights = [[tensors[n] for n in self.names(e)] for e in range(self.experts)]
+
+        def forward(self, h):
+            choice = (h.float() @ self.router.T).argmax(-1)          # router logits in 32-bit
+            out = torch.zeros_like(h)
+            for e, (gate, up, down) in enumerate(self.weights):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    x = h[rows].contiguous()
+                    act = torch.nn.functional.silu(self.runtime.linear(x, gate)) * self.runtime.linear(x, up)
+                    out[rows] = self.runtime.linear(act, down)
+            return out
+
+    class ToyConfig:
+        architecture, model_type = "ToyRoutedForCausalLM", "toy_routed"
+
+        def __init__(self, raw):
+            self.raw = raw
+
+        @classmethod
+        def from_hf_dict(cls, raw):
+            return cls(raw)
+
+        def to_hf_dict(self):
+            return self.raw
+
+    def toy_model_spec(cfg):
+        raw = cfg.raw
+        hidden = raw["hidden_size"]
+        norm = lambda name: PartSpec("rmsnorm", {"dim": hidden, "eps": raw["eps"], "weight": name})
+        position = PartSpec("scaled_rotary", {"dim": raw["head_dim"], "theta": 5000.0, "factor": 4.0})
+        layers = []
+        for i in range(raw["layers"]):
+            layers.append(LayerSpec(PartSpec("pre_norm", {
+                "input_norm": norm("n1.weight"),
+                "mixer": PartSpec("attention", {"hidden": hidden, "q_heads": raw["q_heads"], "kv_heads": raw["kv_heads"],
+                                                "head_dim": raw["head_dim"], "qk_norm_eps": None, "position": position}),
+                "post_norm": norm("n2.weight"),
+                "feed_forward": PartSpec("routed", {"hidden": hidden, "inter": raw["inter"], "experts": 3})}), f"blocks.{i}."))
+        return ModelSpec("ToyRoutedForCausalLM", raw["vocab_size"], hidden, 4096, "tok.weight", norm("final.weight"), None, layers)
+
+    register_position("scaled_rotary", ScaledRotary)
+    register_feed_forward("routed", Routed)
+    register_architecture("ToyRoutedForCausalLM", "toy_routed", ToyConfig, toy_model_spec)
+    try:
+        raw = {"architectures": ["ToyRoutedForCausalLM"], "model_type": "toy_routed", "vocab_size": 60, "hidden_size": 40,
+               "inter": 56, "layers": 2, "eps": 1e-5, "q_heads": 3, "kv_heads": 1, "head_dim": 16}
+        lb.write_model_folder(ToyConfig(raw), tmp_path, seed=8, std=0.3, norm_std=0.1, store_dtype=torch.float32)
+        model = lb.load_model(tmp_path, device="cuda", dtype="fp32")
+
+        def plain(tokens):
+            from safetensors.torch import load_file
+            w = load_file(str(tmp_path / "model.safetensors"))
+            x = w["tok.weight"][torch.tensor(tokens)]
+            n = len(tokens)
+            cos, sin = plain_rope_tables(torch.arange(n).float() / 4.0, 16, 5000.0, torch.float32)
+            for i in range(2):
+                p = f"blocks.{i}."
+                h = plain_rmsnorm(x, w[p + "n1.weight"], 1e-5)
+                q = plain_linear(h, w[p + "self_attn.q_proj.weight"]).view(n, 3, 16)
+                k = plain_linear(h, w[p + "self_attn.k_proj.weight"]).view(n, 1, 16)
+                v = plain_linear(h, w[p + "self_attn.v_proj.weight"]).view(n, 1, 16)
+                q, k = plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin)
+                x = x + plain_linear(plain_attention(q, k, v).reshape(n, -1), w[p + "self_attn.o_proj.weight"])
+                h = plain_rmsnorm(x, w[p + "n2.weight"], 1e-5)
+                choice = (h @ w[p + "mlp.router.weight"].T).argmax(-1)
+                routed = torch.zeros_like(h)
+                for e in range(3):
+                    rows = choice == e
+                    routed[rows] = plain_mlp(h[rows], *(w[f"{p}mlp.experts.{e}.{name}.weight"] for name in ("gate", "up", "down")))
+                x = x + routed
+            return plain_rmsnorm(x, w["final.weight"], 1e-5) @ w["tok.weight"].T
+
+        tokens = random_prompt(60, 37, 5)
+        expected = plain(tokens)
+        for cuts in ([37], [5, 2, 16, 14], [20] + [1] * 17):
+            got, cache, seq = step_in_portions(model, tokens, 4, cuts, blocks=16)
+            assert (got - expected).abs().max() <= tolerance(expected, torch.float32), cuts
+            cache.close(seq)
+    finally:
+        unregister("position", "scaled_rotary")
+        unregister("feed_forward", "routed")
+        unregister_architecture("ToyRoutedForCausalLM")
+
