@@ -139,6 +139,63 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delt
   }
 }
 
+// The same for many rows whose width is exactly one 16-byte piece per thread: a block takes RPB rows
+// at once, issues the loads of all of them before any arithmetic and keeps the values in registers.
+// Every row's sums are taken in the order of the kernel above, so the results are the same bits.
+template <typename T, int RPB>
+__global__ void add_rmsnorm_rows_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ weight,
+                                        T* __restrict__ out, int n_rows, int hidden, float eps) {
+  constexpr int N = Pack<T>::N;
+  __shared__ float scratch[RPB][33];
+  pdl_launch_dependents();
+  const int i = threadIdx.x * N, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float w[N];
+#pragma unroll
+  for (int j = 0; j < N; j += 4) Pack<float>::load(weight + i + j, *reinterpret_cast<float(*)[4]>(&w[j]));   // weights: no kernel writes them
+  pdl_wait();
+  float v[RPB][N], d[RPB][N], ss[RPB];
+#pragma unroll
+  for (int r = 0; r < RPB; ++r) {
+    const size_t row = (size_t)blockIdx.x * RPB + r;
+#pragma unroll
+    for (int j = 0; j < N; ++j) v[r][j] = d[r][j] = 0.f;
+    if (row < (size_t)n_rows) {
+      Pack<T>::load(x + row * hidden + i, v[r]);
+      if (delta) Pack<T>::load(delta + row * hidden + i, d[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RPB; ++r) {
+    const size_t row = (size_t)blockIdx.x * RPB + r;
+    if (delta) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[r][j] = Elem<T>::round(v[r][j] + d[r][j]);
+      if (row < (size_t)n_rows) Pack<T>::store(x + row * hidden + i, v[r]);
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; ++j) sum += v[r][j] * v[r][j];
+    sum = warp_sum(sum);
+    if (lane == 0) scratch[r][warp] = sum;
+  }
+  __syncthreads();
+  if (threadIdx.x < RPB) {
+    float total = 0.f;
+    for (int k = 0; k < nwarps; ++k) total += scratch[threadIdx.x][k];
+    scratch[threadIdx.x][32] = total;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < RPB; ++r) {
+    const size_t row = (size_t)blockIdx.x * RPB + r;
+    ss[r] = scratch[r][32];
+    const float inv = 1.0f / sqrtf(ss[r] / (float)hidden + eps);
+#pragma unroll
+    for (int j = 0; j < N; ++j) v[r][j] = w[j] * Elem<T>::round(v[r][j] * inv);
+    if (row < (size_t)n_rows) Pack<T>::store(out + row * hidden + i, v[r]);
+  }
+}
+
 template <typename T>
 static int launch_add_rmsnorm(void* x, const void* delta, const float* weight, void* out, const int* rows, int n_rows,
                               int hidden, float eps, size_t smem, cudaStream_t stream) {
@@ -149,6 +206,12 @@ static int launch_add_rmsnorm(void* x, const void* delta, const float* weight, v
   int threads = vec ? ((hidden / N + 31) / 32) * 32 : (hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128));
   if (threads > 512) threads = 512;
   if (threads < 32) threads = 32;
+  if (vec && !rows && n_rows >= 256 && hidden == threads * N && (uintptr_t)weight % 16 == 0) {
+    constexpr int RPB = 2;
+    lb_launch(add_rmsnorm_rows_kernel<T, RPB>, (n_rows + RPB - 1) / RPB, threads, 0, stream, (T*)x, (const T*)delta, weight,
+              (T*)out, n_rows, hidden, eps);
+    return lb_last_error();
+  }
   if (vec) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
