@@ -20,7 +20,7 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager
 from ..profiling import nvtx_range
-from .batch import BatchBuilder, BatchCapacity, StepBatch, StepEntry
+from .batch import BatchBuilder, BatchCapacity, StepEntry
 
 DEFAULT_GRAPH_SIZES = (1, 2, 4, 8, 16, 32, 64)
 

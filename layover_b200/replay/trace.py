@@ -39,7 +39,6 @@ def parse_args(argv=None):
 
 
 def run(args, lines, say=print) -> int:
-    import numpy as np
     import torch
 
     from .. import PagedKVCache, load_model
