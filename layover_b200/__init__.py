@@ -20,8 +20,9 @@ import torch
 
 from .cache import CacheManager, OutOfBlocks
 from .config import Qwen3Config, load_config, preset, register_architecture, supported_architectures
-from .engine import Engine, EngineConfig, Request, RequestTooLarge, State, StepEntry
+from .engine import DEVICE_TOKEN, Engine, EngineConfig, Request, RequestTooLarge, State, StepEntry
 from .models import load_model, random_model
+from .parts.base import PagedKVNeed
 from .sampling import SamplingParams
 from .weights import write_model_folder
 
@@ -31,21 +32,22 @@ __version__ = "0.1.0"
 def PagedKVCache(model, num_blocks: int, device=None, dtype=None, block_tokens: int = 16,
                  max_requests: int = 64) -> CacheManager:
     """The cache for `model`: `num_blocks` pages of `block_tokens` tokens for each group of layers
-    with the same needs, plus `max_requests` slots of per-request state. Device and dtype default
-    to the model's (argument order of layover/kv/paged_cache.py:27-34)."""
+    with the same needs, plus `max_requests` slots of per-request state (the mixers' own and the
+    record the sampler keeps). Device and dtype default to the model's (argument order of
+    layover/kv/paged_cache.py:27-34)."""
+    from . import ops
+
     device = model.device if device is None else device
     dtype = model.dtype if dtype is None else dtype
-    return CacheManager(model.cache_needs(), num_blocks, block_tokens, dtype, device, max_requests)
+    return CacheManager(model.cache_needs(), num_blocks, block_tokens, dtype, device, max_requests, ops.RECORD_WORDS)
 
 
 def blocks_for_pool(model, pool_gib: float, block_tokens: int = 16) -> int:
     """Pages that fit a pool of `pool_gib` GiB (layover/server.py:445-447)."""
-    bytes_per_token = 0
     element = torch.empty((), dtype=model.dtype).element_size()
-    for _, need, reads in model.cache_needs():
-        if reads is None and hasattr(need, "kv_heads"):
-            bytes_per_token += 2 * need.kv_heads * need.head_dim * element
-    return max(1, int(pool_gib * 2**30 / (bytes_per_token * block_tokens)))
+    bytes_per_token = sum(need.elements_per_token() * element for _, need, reads in model.cache_needs()
+                          if reads is None and isinstance(need, PagedKVNeed))
+    return max(1, int(pool_gib * 2**30 / (max(bytes_per_token, 1) * block_tokens)))
 
 
 def generate(model, prompts: list[list[int]], max_new_tokens: int = 16, temperature: float = 0.0, seed: int = 0,
@@ -68,7 +70,7 @@ def generate(model, prompts: list[list[int]], max_new_tokens: int = 16, temperat
 
 __all__ = [
     "CacheManager", "OutOfBlocks", "Qwen3Config", "load_config", "preset", "register_architecture",
-    "supported_architectures", "Engine", "EngineConfig", "Request", "RequestTooLarge", "State", "StepEntry",
+    "supported_architectures", "DEVICE_TOKEN", "Engine", "EngineConfig", "Request", "RequestTooLarge", "State", "StepEntry",
     "load_model", "random_model", "SamplingParams", "write_model_folder", "PagedKVCache", "blocks_for_pool",
     "generate",
 ]

@@ -6,8 +6,9 @@
 Option names and meanings follow the reference's server where it has them
 (layover/server.py:415-434): --model, --device, --dtype {bf16,fp32}, --pool-gib, --block-tokens,
 --max-batch, --prefill-chunk (also the per-step prompt budget, as server.py:461), --cuda-graphs.
-The HTTP server itself and the agent options are not part of this engine. The result is one JSON
-object on standard output.
+--ignore-eos is the request option of that name (server.py:183,195). --max-batched-tokens is this
+engine's own: one budget for a whole step, decoded tokens first. The HTTP server itself and the
+agent options are not part of this engine. The result is one JSON object on standard output.
 """
 
 from __future__ import annotations
@@ -31,6 +32,10 @@ def parse_args(argv=None):
     p.add_argument("--block-tokens", type=int, default=16)
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--prefill-chunk", type=int, default=512)
+    p.add_argument("--max-batched-tokens", type=int, default=None,
+                   help="most tokens of a whole step, decoded tokens first (default: --prefill-chunk prompt tokens a "
+                        "step, decoded tokens not counted)")
+    p.add_argument("--ignore-eos", action="store_true", help="generate --max-new-tokens whatever is sampled")
     p.add_argument("--cuda-graphs", action="store_true", help="replay decode steps from CUDA graphs")
     p.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids; may repeat")
     p.add_argument("--prompt-lens", default=None, help="comma-separated lengths of seeded random prompts")
@@ -71,11 +76,12 @@ def main(argv=None) -> int:
         raise SystemExit("no prompts: give --prompt-ids or --prompt-lens")
     blocks = args.num_blocks or lb.blocks_for_pool(model, args.pool_gib, args.block_tokens)
     cache = lb.PagedKVCache(model, blocks, block_tokens=args.block_tokens, max_requests=max(args.max_batch, 1))
-    engine = lb.Engine(model, cache, lb.EngineConfig(args.max_batch, args.prefill_chunk, args.prefill_chunk),
-                       cuda_graphs=args.cuda_graphs)
+    engine = lb.Engine(model, cache, lb.EngineConfig(args.max_batch, args.prefill_chunk, args.prefill_chunk,
+                                                     args.max_batched_tokens), cuda_graphs=args.cuda_graphs)
     stop = frozenset() if getattr(model.cfg, "eos_token_id", None) is None else frozenset({model.cfg.eos_token_id})
     for index, prompt in enumerate(prompts):
-        engine.add_request(lb.Request(str(index), prompt, args.max_new_tokens, stop, args.temperature, args.seed + index))
+        engine.add_request(lb.Request(str(index), prompt, args.max_new_tokens, stop, args.temperature, args.seed + index,
+                                      ignore_eos=args.ignore_eos))
     began = time.perf_counter()
     finished = {r.request_id: r for r in engine.run_until_idle()}
     torch.cuda.synchronize()

@@ -15,6 +15,14 @@ A group with a window only keeps the pages that a later query can still see: aft
 pages that lie wholly below `tokens - window + 1` go back to the free list and are reused.
 State groups own `[slots + 1, *shape]`; a request's slot is zeroed when it is opened.
 
+Beside the mixers' state every request has one *record* of `record_words` int32 words on the
+device, `records[slot]`, written whole when the request is opened and never touched by the host
+again: kernels index it by the request's slot, so a captured CUDA graph sees a fixed address.
+What the words mean is the business of whoever writes and reads them (the sampler keeps the
+request's seed, counter, temperature and last token there); the manager only hands out the row.
+(The reference keeps such facts on the host, layover/engine.py:39-40; its nearest device-side
+relative is the packed row at a fixed address of layover/decode_graphs.py:56-77.)
+
 All bookkeeping is on the host and works without a device (`device=None` allocates no pools),
 which is how the scheduler and the property tests use it.
 """
@@ -83,7 +91,7 @@ class SequenceCache:
 class CacheManager:
     def __init__(self, needs: list[tuple[int, object, int | None]], num_blocks: int, block_tokens: int = 16,
                  dtype: torch.dtype = torch.bfloat16, device: torch.device | str | None = None,
-                 max_requests: int = 64):
+                 max_requests: int = 64, record_words: int = 8):
         """`needs`: for every schedule entry (entry index, its need or None, the entry whose cache
         it reads instead of its own or None). `num_blocks` pages per paged group."""
         if block_tokens <= 0:
@@ -123,6 +131,10 @@ class CacheManager:
                                               page_tokens=block_tokens, need=src.need)
         self._slots = BlockAllocator(max_requests)
         self.live: dict[str, SequenceCache] = {}
+        self.record_words = int(record_words)
+        self.records: torch.Tensor | None = None     # [max_requests + 1, record_words] int32 on the device
+        self._record_staging = None                  # the same rows in pinned host memory, and when each was last sent
+        self._record_sent: list = [None] * (max_requests + 1)
         if self.device is not None:
             self._allocate_pools()
 
@@ -136,6 +148,10 @@ class CacheManager:
         for group in self.states:
             group.pool = torch.zeros((len(group.entries), self.max_requests + 1, *group.need.shape),
                                      dtype=group.need.dtype, device=self.device)
+        self.records = torch.zeros((self.max_requests + 1, self.record_words), dtype=torch.int32, device=self.device)
+        if self.device.type == "cuda":
+            self._record_staging = torch.zeros((self.max_requests + 1, self.record_words), dtype=torch.int32,
+                                               pin_memory=True)
         for view in self.views.values():
             if view.kind == "paged":
                 pool = self.paged[view.group].pool
@@ -150,8 +166,12 @@ class CacheManager:
     def scratch_slot(self) -> int:
         return self.max_requests
 
+    @property
+    def num_free_slots(self) -> int:
+        return self._slots.num_free
+
     def pool_bytes(self) -> int:
-        pools = [g.pool for g in self.paged] + [g.pool for g in self.states]
+        pools = [g.pool for g in self.paged] + [g.pool for g in self.states] + [self.records]
         return sum(p.numel() * p.element_size() for p in pools if p is not None)
 
     # ------------------------------------------------------------------ arithmetic
@@ -190,9 +210,13 @@ class CacheManager:
         return out
 
     # ------------------------------------------------------------------ life of a request
-    def open(self, request_id: str) -> SequenceCache:
+    def open(self, request_id: str, record: list[int] | None = None) -> SequenceCache:
+        """A slot and empty tables for a new request. `record` (up to `record_words` int32 values, the
+        rest zero) becomes the request's record on the device; the mixers' state of the slot is zeroed."""
         if request_id in self.live:
             raise ValueError(f"request {request_id!r} is already open")
+        if record is not None and len(record) > self.record_words:
+            raise ValueError(f"a record holds {self.record_words} words, got {len(record)}")
         try:
             slot = self._slots.alloc(1)[0]
         except OutOfBlocks:
@@ -200,6 +224,20 @@ class CacheManager:
         for group in self.states:
             if group.pool is not None:
                 group.pool[:, slot].zero_()
+        if self.records is not None:
+            words = torch.zeros(self.record_words, dtype=torch.int32)
+            if record:
+                words[: len(record)] = torch.tensor(record, dtype=torch.int64).to(torch.int32)
+            if self._record_staging is not None:
+                # stream-ordered behind every kernel that still uses the slot's previous owner
+                if self._record_sent[slot] is not None:
+                    self._record_sent[slot].synchronize()
+                self._record_staging[slot] = words
+                self.records[slot].copy_(self._record_staging[slot], non_blocking=True)
+                self._record_sent[slot] = torch.cuda.Event()
+                self._record_sent[slot].record()
+            else:
+                self.records[slot] = words
         seq = SequenceCache(request_id, slot, [BlockTable() for _ in self.paged])
         self.live[request_id] = seq
         return seq
@@ -255,12 +293,41 @@ class CacheManager:
     release = close
 
     # ------------------------------------------------------------------ checks
-    def check_tables(self, seq: SequenceCache) -> None:
-        """What a kernel cannot check for itself (layover/kv/paged_cache.py:160-165)."""
+    def check_tables(self, seq: SequenceCache, tokens: int | None = None) -> None:
+        """What a kernel cannot check for itself, before every launch (layover/kv/paged_cache.py:160-165):
+        the request is the one this manager opened, its slot is inside the pool, every page id of
+        its tables is inside its group's pool and held (or the scratch page), and the tables cover
+        `tokens` tokens (default: those it holds)."""
+        if self.live.get(seq.request_id) is not seq:
+            raise ValueError(f"request {seq.request_id!r} is not open in this cache")
+        if not 0 <= seq.slot < self.max_requests or len(seq.tables) != len(self.paged):
+            raise ValueError(f"request {seq.request_id!r}: slot {seq.slot} or its tables do not belong to this cache")
+        needed = self.blocks_for(seq.num_tokens if tokens is None else tokens)
         for group, table in zip(self.paged, seq.tables):
+            if len(table.blocks) < needed:
+                raise ValueError(f"request {seq.request_id!r}: {needed} pages needed, its table has {len(table.blocks)}")
+            held = group.allocator.is_held
             for block in table.blocks:
-                if block != group.scratch_page and not group.allocator.is_held(block):
-                    raise ValueError(f"request {seq.request_id!r}: block {block} is not allocated")
+                if block != group.scratch_page and not held(block):
+                    raise ValueError(f"request {seq.request_id!r}: block {block} is not an allocated page of its pool")
+
+    def check_row(self, group_index: int, row, request_id: str = "?") -> None:
+        """The same check on one request's page ids as an int32 numpy array (what the batch builder
+        is about to send to the device): every id is the scratch page or a held page of the group's
+        pool. Vectorised, so that it costs little on every step."""
+        import numpy as np
+
+        group = self.paged[group_index]
+        if row.size == 0:
+            return
+        low, high = int(row.min()), int(row.max())
+        if low < 0 or high > group.scratch_page:
+            raise ValueError(f"request {request_id!r}: page id {low if low < 0 else high} is outside its pool of "
+                             f"{group.allocator.num_blocks} pages")
+        real = row[row != group.scratch_page]
+        if real.size and not np.frombuffer(group.allocator._out, dtype=np.uint8)[real].all():
+            bad = int(real[np.frombuffer(group.allocator._out, dtype=np.uint8)[real] == 0][0])
+            raise ValueError(f"request {request_id!r}: block {bad} is not an allocated page of its pool")
 
     def check(self) -> None:
         """No page lost, held twice or both free and held, over all live requests."""

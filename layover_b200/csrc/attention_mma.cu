@@ -546,7 +546,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         acc += recv_acc[(size_t)s2 * per + k] * f;
         l_all += recv_ml[((size_t)s2 * group + r) * 2 + 1] * f;
       }
-      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(acc / l_all);
+      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
     }
     return;
   }
@@ -567,7 +567,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
       l_all += src[dim + 1] * f;
     }
     if (splits == 1) {
-      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(acc / l_all);
+      out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
     } else {
       my_partial[r * mstride + col] = acc;
       if (col == 0) { my_partial[r * mstride + dim] = m_all; my_partial[r * mstride + dim + 1] = l_all; }
@@ -614,7 +614,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     float acc = 0.f;
 #pragma unroll 8
     for (int s = 0; s < splits; ++s) acc += all[((size_t)s * group + r) * mstride + col] * factor[s * group + r];
-    out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(acc / l_total[r]);
+    out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(l_total[r] > 0.f ? acc / l_total[r] : 0.f);
   }
   if (threadIdx.x == 0) counters[tile_id] = 0;
 }
@@ -638,9 +638,9 @@ namespace {
 template <typename Kernel> void allow_smem(Kernel kernel, size_t bytes) {
   cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
-void configure_once() {
-  static bool done = false;
-  if (done) return;
+void configure_once() {      // once per device: the attribute belongs to the device that is current
+  static LbPerDeviceOnce once;
+  if (!once.first()) return;
   allow_smem(attention_prefill_kernel<128, true>, prefill_smem(128));
   allow_smem(attention_prefill_kernel<128, false>, prefill_smem(128));
   allow_smem(attention_prefill_kernel<256, true>, prefill_smem(256));
@@ -652,7 +652,6 @@ void configure_once() {
   allow_smem(attention_decode_kernel<256, false, true>, decode_smem(256));
   allow_smem(attention_decode_kernel<128, true, false, true>, decode_smem(128));
   allow_smem(attention_decode_kernel<128, true, true, true>, decode_smem(128));
-  done = true;
 }
 
 // launches the decode kernel instantiation for this head size and group
@@ -712,7 +711,7 @@ LB_EXPORT long lb_attention_decode_scratch(int n_seqs, int q_heads, int dim, int
 }
 
 // Sequences with one new token each. `seq_list` (n_seqs indices into cu_q / ctx_len / block_table)
-// may be null for "all of them in order". `counters` (n_seqs * kv_heads, zero between launches) and
+// may be null for "all of them in order". A sequence whose ctx_len is 0 (no key at all) gets zeros. `counters` (n_seqs * kv_heads, zero between launches) and
 // `partials` are needed when splits > 1.
 LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
                                        const int* block_table, int table_width, const int* cu_q, const int* ctx_len,

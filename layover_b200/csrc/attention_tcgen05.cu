@@ -826,12 +826,11 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-void configure_once() {
-  static bool done = false;
-  if (done) return;
+void configure_once() {      // once per device: the attribute belongs to the device that is current
+  static LbPerDeviceOnce once;
+  if (!once.first()) return;
   cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   cudaFuncSetAttribute(attention_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
-  done = true;
 }
 
 // q as a 2-D bf16 matrix [rows, cols] with rows `stride` elements apart: box 64 columns x 128 rows
@@ -874,6 +873,14 @@ LB_EXPORT int lb_attention_tcgen05_pool_map(void* out, const void* pool, long pl
     return LB_ERR_SIZE;
   memcpy(out, &map, sizeof(map));
   return 0;
+}
+
+// The device address of the error word, so that a caller's own kernel can read it along with its
+// results instead of synchronising for it (null if it cannot be had).
+LB_EXPORT void* lb_attention_tcgen05_status_address() {
+  void* address = nullptr;
+  if (cudaGetSymbolAddress(&address, g_attn_error) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  return address;
 }
 
 LB_EXPORT int lb_attention_tcgen05_status() {

@@ -6,6 +6,11 @@ written). The hash covers the source, the headers of this folder and the compile
 outdated library is never loaded. A library is built the first time one of its functions is
 wanted; `ensure_built(names)` builds several in parallel and prints a line every few seconds
 while nvcc runs. Nothing here needs a home directory, a network or a GPU.
+
+A part that lives outside this package brings its own kernels with `register_source(name,
+path)`: the file is compiled with the same flags (and `-I` this folder, so it may include
+`common.cuh`), hashed and loaded like the package's own, and the part names the library in its
+`kernel_libraries()`.
 """
 
 from __future__ import annotations
@@ -24,7 +29,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 
-# name -> (source file, extra link flags)
+# name -> (source file, relative to this folder or absolute; extra link flags)
 SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "elementwise": ("elementwise.cu", ()),
     "gemm_simt": ("gemm_simt.cu", ()),
@@ -52,8 +57,29 @@ class ExtensionError(RuntimeError):
     """The CUDA extension could not be built or loaded. There is no fallback path."""
 
 
+def register_source(name: str, path: str | Path, link_flags: tuple[str, ...] = (),
+                    includes: tuple[str | Path, ...] = ()) -> None:
+    """Make the .cu file at `path` (anywhere on disk) loadable as library `name`. `includes` lists
+    further files whose text it includes, so that a change to them rebuilds it. Registering the same
+    name and path again is a no-op; a package library's name cannot be taken over."""
+    path = Path(path).resolve()
+    if not path.is_file():
+        raise ExtensionError(f"kernel source {path} does not exist")
+    known = SOURCES.get(name)
+    if known is not None and _source_path(name) != path:
+        raise ExtensionError(f"kernel library {name!r} is already registered from {_source_path(name)}")
+    SOURCES[name] = (str(path), tuple(link_flags))
+    if includes:
+        INCLUDED_SOURCES[name] = tuple(str(Path(p).resolve()) for p in includes)
+
+
+def _source_path(name: str) -> Path:
+    return (HERE / SOURCES[name][0]).resolve()      # an absolute entry stays as it is
+
+
 def available_sources() -> list[str]:
-    return [name for name, (src, _) in SOURCES.items() if (HERE / src).is_file()]
+    """The package's own sources (those inside this folder)."""
+    return [name for name in SOURCES if _source_path(name).is_file() and _source_path(name).parent == HERE]
 
 
 def _nvcc() -> str:
@@ -66,7 +92,7 @@ def _nvcc() -> str:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS + SOURCES[name][1]).encode())
-    h.update((HERE / SOURCES[name][0]).read_bytes())
+    h.update(_source_path(name).read_bytes())
     for included in INCLUDED_SOURCES.get(name, ()):
         h.update((HERE / included).read_bytes())
     for header in sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h")):
@@ -111,6 +137,10 @@ def library_path(name: str) -> Path:
     return build_dir() / filename
 
 
+def is_package_source(name: str) -> bool:
+    return _source_path(name).parent == HERE
+
+
 def _say(message: str) -> None:
     print(f"[layover_b200] {message}", file=sys.stderr, flush=True)
 
@@ -119,9 +149,10 @@ def _compile(name: str) -> Path:
     target = library_path(name)
     if target.is_file():
         return target
-    source, link = SOURCES[name]
+    source, link = _source_path(name), SOURCES[name][1]
     partial = target.with_name(f".{target.name}.{os.getpid()}.{threading.get_ident()}.tmp")
-    command = [_nvcc(), *NVCC_FLAGS, "-o", str(partial), str(HERE / source), *link]
+    command = [_nvcc(), *NVCC_FLAGS, "-I", str(HERE), "-o", str(partial), str(source), *link]
+    source = source.name
     _say(f"compiling {source} for sm_100a (first use) ...")
     began = time.monotonic()
     with tempfile.TemporaryFile() as log:
@@ -171,6 +202,11 @@ def load(name: str) -> ctypes.CDLL:
                 raise ExtensionError(f"cannot load {path}: {error}") from error
             _loaded[name] = lib
     return lib
+
+
+def loaded() -> tuple[str, ...]:
+    """Names of the libraries this process has loaded so far."""
+    return tuple(_loaded)
 
 
 def build_all() -> list[Path]:

@@ -20,6 +20,18 @@ enum LbDtype { LB_F32 = 0, LB_BF16 = 1 };
 
 typedef __nv_bfloat16 bf16;
 
+// A request's record of fixed size on the device: int32 words, one row per state slot. Written
+// whole when the request is admitted; the sampling kernel reads seed, counter and temperature,
+// stores the token it chose and bumps the counter; the embedding kernel reads the last token of
+// rows whose token the host has not seen yet.
+#define LB_RECORD_WORDS 8
+#define LB_RECORD_POSITION 0      // tokens the request holds once its newest sampled token is counted
+#define LB_RECORD_SEED_LO 1
+#define LB_RECORD_SEED_HI 2
+#define LB_RECORD_COUNT 3         // tokens sampled so far
+#define LB_RECORD_TEMPERATURE 4   // float bits; 0 = greedy
+#define LB_RECORD_LAST_TOKEN 5
+
 template <typename T> struct Elem;
 template <> struct Elem<float> {
   static __device__ __forceinline__ float load(const float* p) { return *p; }
@@ -62,6 +74,25 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 static inline int lb_last_error() { return (int)cudaGetLastError(); }
+
+// Function attributes (the raised shared-memory limit of a kernel) belong to a device, not to the
+// process: `first()` is true once per device, for the device that is current at the call.
+struct LbPerDeviceOnce {
+  static constexpr int MAX_DEVICES = 64;
+  bool done[MAX_DEVICES] = {};
+  int current() const {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return -1;
+    return device;
+  }
+  bool first() {
+    const int device = current();
+    if (device < 0) return true;          // unknown device: configure again rather than not at all
+    if (done[device]) return false;
+    done[device] = true;
+    return true;
+  }
+};
 
 // ---- programmatic dependent launch
 // Every kernel of this package is launched so that it may start while its predecessor in the

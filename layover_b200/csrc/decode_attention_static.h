@@ -18,8 +18,9 @@
 //
 // Things to know:
 //   * Every GPU whose context loads this library holds the array until the process exits.
-//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
-//     raises the kernel's shared-memory limit; make that first call outside any stream capture.
+//   * The first call on each device, with that device current, looks up the array's address there
+//     (cudaGetSymbolAddress) and raises the kernels' shared-memory limit on it; make that first call
+//     outside any stream capture, and from one host thread at a time.
 //   * All calls share the array and it keeps what the last call left. Each call clears the
 //     counters it is about to use (a memset on the caller's stream), so a call that was torn
 //     down half-way cannot poison the next. Two calls that overlap on the GPU (different streams
@@ -43,7 +44,11 @@ extern "C" {
 
 // out[row, head, :] = attention of the single new token of each of `n_seqs` sequences over its
 // paged keys and values (bfloat16, head size a multiple of 16 up to 256, at most 16 query heads per
-// KV head). Same arguments and result as `lb_attention_decode_bf16` without the scratch pointers.
+// KV head). The arguments of `lb_attention_decode_bf16` without the scratch pointers and without
+// `seq_list` (every sequence is served, in order). The result is that entry point's up to the order
+// in which the splits are added: bit-identical wherever the regular entry merges through scratch
+// memory too, and within rounding of it for head size 128 with 2, 4 or 8 splits, where the regular
+// entry merges inside a thread-block cluster. A sequence whose ctx_len is 0 gets zeros.
 // Returns 0, a cudaError_t (> 0) from the launch, or one of LB_STATIC_ERR_*.
 int lb_attention_decode_bf16_static(const void* q, const void* k_pool, const void* v_pool, void* out,
                                     const int* block_table, int table_width, const int* cu_q, const int* ctx_len,

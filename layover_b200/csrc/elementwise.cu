@@ -5,43 +5,45 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// x[t, :] = table[ids[t], :]   (layover/model.py:219,247: no scaling)
+// x[t, :] = table[id, :]   (layover/model.py:219,247: no scaling). The id is ids[t], or, where
+// token_src[t] >= 0, the last token in record token_src[t] of the per-request records: a step may
+// be launched before the host has read the token that the step before it sampled.
 template <typename T>
-__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ x,
-                             int hidden) {
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ token_src,
+                             const int* __restrict__ records, const T* __restrict__ table, T* __restrict__ x,
+                             int hidden, int vocab) {
   pdl_launch_dependents();
   pdl_wait();
-  const T* src = table + (size_t)ids[blockIdx.x] * hidden;
+  int id = ids[blockIdx.x];
+  if (token_src && records) {
+    const int slot = token_src[blockIdx.x];
+    if (slot >= 0) id = records[(size_t)slot * LB_RECORD_WORDS + LB_RECORD_LAST_TOKEN];
+  }
+  id = min(max(id, 0), vocab - 1);    // a record that was never sampled into cannot index outside the table
+  const T* src = table + (size_t)id * hidden;
   T* dst = x + (size_t)blockIdx.x * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+  if (sizeof(T) * hidden % 16 == 0 && ((uintptr_t)table % 16 == 0) && ((uintptr_t)x % 16 == 0)) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    const int n = (int)(sizeof(T) * hidden / 16);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+  }
 }
 
-LB_EXPORT int lb_embed(int dtype, const int* ids, const void* table, void* x, int tokens, int hidden,
-                       cudaStream_t stream) {
+LB_EXPORT int lb_embed(int dtype, const int* ids, const int* token_src, const int* records, const void* table, void* x,
+                       int tokens, int hidden, int vocab, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (vocab <= 0) return LB_ERR_SIZE;
   if (dtype == LB_F32)
-    lb_launch(embed_kernel<float>, tokens, 256, 0, stream, ids, (const float*)table, (float*)x, hidden);
+    lb_launch(embed_kernel<float>, tokens, 256, 0, stream, ids, token_src, records, (const float*)table, (float*)x, hidden,
+              vocab);
   else if (dtype == LB_BF16)
-    lb_launch(embed_kernel<bf16>, tokens, 256, 0, stream, ids, (const bf16*)table, (bf16*)x, hidden);
+    lb_launch(embed_kernel<bf16>, tokens, 256, 0, stream, ids, token_src, records, (const bf16*)table, (bf16*)x, hidden,
+              vocab);
   else
     return LB_ERR_DTYPE;
-  return lb_last_error();
-}
-
-// ---------------------------------------------------------------- tokens that are still on the device
-// ids[t] = previous[source[t]] where source[t] >= 0: a step may be launched before the host has read
-// the tokens that the step before it sampled; those rows take their token from the sampler's output.
-__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ previous,
-                                    int tokens) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < tokens && source[t] >= 0) ids[t] = previous[source[t]];
-}
-
-LB_EXPORT int lb_patch_tokens(int* ids, const int* source, const int* previous, int tokens, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
-  lb_launch(patch_tokens_kernel, (tokens + 127) / 128, 128, 0, stream, ids, source, previous, tokens);
   return lb_last_error();
 }
 

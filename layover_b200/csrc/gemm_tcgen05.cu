@@ -923,8 +923,9 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
            cudaStream_t stream) {
   using T = Tile<BN, SWAP>;
   auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
-  static int blocks_per_sm = 0;      // how many blocks of this kernel an SM really holds
-  if (blocks_per_sm == 0) {
+  static int blocks_per_sm = 0;      // how many blocks of this kernel an SM really holds (the same on every B200)
+  static LbPerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
       return lb_last_error();
     int fit = 0;
@@ -982,11 +983,10 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
                     cudaStream_t stream) {
   using T = SmallTile<BN>;
   auto kernel = gemm_fewtoken_kernel<BN, OutT, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  static LbPerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
       return lb_last_error();
-    configured = true;
   }
   const int tiles = (pb.rows_a + BM - 1) / BM, total_kb = (pb.K + BK - 1) / BK;
   int splits = 1;
@@ -1010,11 +1010,10 @@ int launch_fewtoken(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C,
     if (splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && lb_cluster_reduce_enabled()) {
       // the K ranges of a tile as one cluster: partial sums travel through distributed shared memory
       auto cluster_kernel = gemm_fewtoken_kernel<BN, OutT, EPI, true>;
-      static bool cluster_configured = false;
-      if (!cluster_configured) {
+      static LbPerDeviceOnce cluster_configured;
+      if (cluster_configured.first()) {
         if (cudaFuncSetAttribute(cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_CLUSTER) != cudaSuccess)
           return lb_last_error();
-        cluster_configured = true;
       }
       const int code = lb_launch_cluster(cluster_kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream,
                                          (unsigned)splits, map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, pb.K,
@@ -1041,11 +1040,10 @@ int launch_heads(const CUtensorMap& map_a, const CUtensorMap& map_b, const Probl
   while (splits & (splits - 1)) splits &= splits - 1;         // down to a power of two
   if (splits < 2 || !lb_cluster_reduce_enabled()) return 1;
   auto kernel = gemm_fewtoken_kernel<BN, bf16, 2, true>;
-  static bool configured = false;
-  if (!configured) {
+  static LbPerDeviceOnce configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_CLUSTER) != cudaSuccess)
       return lb_last_error();
-    configured = true;
   }
   dim3 grid(tiles, 1, splits);
   const int code = lb_launch_cluster(kernel, grid, dim3(SMALL_THREADS), (size_t)T::SMEM_CLUSTER, stream, (unsigned)splits,
@@ -1054,6 +1052,14 @@ int launch_heads(const CUtensorMap& map_a, const CUtensorMap& map_b, const Probl
   return code ? code : lb_last_error();
 }
 }  // namespace
+
+// The device address of the error word, so that a caller's own kernel can read it along with its
+// results instead of synchronising for it (null if it cannot be had).
+LB_EXPORT void* lb_gemm_tcgen05_status_address() {
+  void* address = nullptr;
+  if (cudaGetSymbolAddress(&address, g_gemm_error) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  return address;
+}
 
 // The error code a kernel recorded when one of its bounded waits ran out (0 = none); clears it.
 LB_EXPORT int lb_gemm_tcgen05_status() {

@@ -1,7 +1,7 @@
-from .batch import BatchBuilder, BatchCapacity, StepBatch, StepEntry
+from .batch import DEVICE_TOKEN, BatchBuilder, BatchCapacity, StepBatch, StepEntry
 from .scheduler import Engine, EngineConfig, Request, RequestTooLarge, State
 
-__all__ = ["BatchBuilder", "BatchCapacity", "StepBatch", "StepEntry", "Engine", "EngineConfig", "Request",
+__all__ = ["DEVICE_TOKEN", "BatchBuilder", "BatchCapacity", "StepBatch", "StepEntry", "Engine", "EngineConfig", "Request",
            "RequestTooLarge", "State", "StepFunction"]
 
 

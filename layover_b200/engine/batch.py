@@ -9,7 +9,8 @@ side; the tokens of all entries are laid end to end:
   ctx_len [S]                         the request's length once this step's tokens are in
   state_slots [S]                     the request's slot of fixed-size state
   logit_rows [R]                      flat rows whose logits are returned, in entry / want order
-  token_src [T]                       row of the previous step's sampled tokens a token comes from, or -1
+  row_slots [R]                       the state slot of the request that each of those rows belongs to
+  token_src [T]                       state slot whose record holds the token (still on the device), or -1
   per paged cache group:
     block_table [S, W]                page ids, padded with the group's scratch page
     slot_map [T]                      page * page_tokens + slot where the token's K and V go
@@ -32,10 +33,14 @@ import torch
 from ..cache.manager import CacheManager, SequenceCache
 
 
+DEVICE_TOKEN = -1   # a token id that means: the request's last sampled token, as its record on the device has it
+
+
 @dataclass
 class StepEntry:
-    """`tokens` are token ids; a negative value -(k + 1) stands for "row k of the tokens that the
-    previous step sampled", which are still on the device when this step is launched."""
+    """`tokens` are token ids. `[DEVICE_TOKEN]` stands for the token that was last sampled for this
+    request: it is in the request's record on the device (where the sampling kernel put it), so a
+    step can be launched before the host has read it."""
     seq: SequenceCache
     tokens: list[int]
     want: list[int] = field(default_factory=list)
@@ -65,7 +70,8 @@ class StepBatch:
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
     n_logit_rows: int
-    token_src: torch.Tensor      # per token: row of the previous step's sampled tokens, or -1
+    row_slots: torch.Tensor      # per logit row: the state slot of its request
+    token_src: torch.Tensor      # per token: the state slot whose record holds it, or -1
     device_tokens: bool          # whether any token comes from the device
     groups: list[GroupBatch]
     tiles: dict[int, QueryTiles]
@@ -154,7 +160,7 @@ class BatchBuilder:
         layout = _Layout()
         layout.add("token_ids", n_tokens); layout.add("positions", n_tokens)
         layout.add("cu_q", n_seqs + 1); layout.add("ctx_len", n_seqs); layout.add("state_slots", n_seqs)
-        layout.add("logit_rows", n_rows); layout.add("token_src", n_tokens)
+        layout.add("logit_rows", n_rows); layout.add("row_slots", n_rows); layout.add("token_src", n_tokens)
         for g in range(len(cache.paged)):
             layout.add(f"table{g}", n_seqs, width); layout.add(f"slots{g}", n_tokens)
         tile_lists = {}
@@ -179,27 +185,30 @@ class BatchBuilder:
             offset, _ = layout.fields[name]
             view[offset:offset + len(values)] = values
 
-        tokens_flat, positions, rows, cu = [], [], [], [0]
+        tokens_flat, positions, rows, row_slots, sources, cu = [], [], [], [], [], [0]
         for index, entry in enumerate(entries):
             n = len(entry.tokens)
             for w in entry.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {entry.seq.request_id!r}: wanted place {w} is outside its {n} tokens")
                 rows.append(cu[-1] + w)
+                row_slots.append(entry.seq.slot)
             tokens_flat.extend(entry.tokens)
+            sources.extend(entry.seq.slot if t < 0 else -1 for t in entry.tokens)
             positions.extend(range(starts[index], starts[index] + n))
             cu.append(cu[-1] + n)
         for _ in range(n_seqs - real):   # padding rows: token 0 at position 0 of the scratch page
-            tokens_flat.append(0); positions.append(0); cu.append(cu[-1] + 1)
+            tokens_flat.append(0); positions.append(0); sources.append(-1); cu.append(cu[-1] + 1)
+        slots_of_seqs = [e.seq.slot for e in entries] + [cache.scratch_slot] * (n_seqs - real)
         if capacity:
-            rows = list(range(n_seqs))
+            rows, row_slots = list(range(n_seqs)), slots_of_seqs
         device_tokens = any(t < 0 for t in tokens_flat)
-        put("token_src", [-t - 1 if t < 0 else -1 for t in tokens_flat] if device_tokens else [-1] * n_tokens)
         if device_tokens:
             tokens_flat = [max(t, 0) for t in tokens_flat]
+        put("token_src", sources)
         put("token_ids", tokens_flat); put("positions", positions); put("cu_q", cu); put("ctx_len", ctx_lens)
-        put("state_slots", [e.seq.slot for e in entries] + [cache.scratch_slot] * (n_seqs - real))
-        put("logit_rows", rows)
+        put("state_slots", slots_of_seqs)
+        put("logit_rows", rows); put("row_slots", row_slots)
         for g, group in enumerate(cache.paged):
             scratch = group.scratch_page
             offset, _ = layout.fields[f"table{g}"]
@@ -216,6 +225,7 @@ class BatchBuilder:
                             f"request {entry.seq.request_id!r}: {ctx_lens[index]} tokens need {needed} pages, "
                             f"its table has {len(blocks)} and the batch is {width} wide")
                     row[:needed] = blocks[:needed]
+                    cache.check_row(g, row[:needed], entry.seq.request_id)     # no bad page id reaches a kernel
                     for pos in range(starts[index], ctx_lens[index]):
                         slots.append(blocks[pos // page] * page + pos % page)
                 else:
@@ -251,7 +261,7 @@ class BatchBuilder:
             n_tokens=n_tokens, n_seqs=n_seqs,
             token_ids=get("token_ids"), positions=get("positions"), cu_q=get("cu_q"), ctx_len=get("ctx_len"),
             state_slots=get("state_slots"), logit_rows=get("logit_rows"), n_logit_rows=n_rows,
-            token_src=get("token_src"), device_tokens=device_tokens,
+            row_slots=get("row_slots"), token_src=get("token_src"), device_tokens=device_tokens,
             groups=[GroupBatch(get(f"table{g}"), get(f"slots{g}")) for g in range(len(cache.paged))],
             tiles={size: QueryTiles(get(f"tile_seq{size}"), get(f"tile_q0{size}"), len(tiles))
                    for size, tiles in tile_lists.items()},
@@ -268,7 +278,7 @@ class BatchBuilder:
         """Upper bound of the int32 words a fixed-capacity batch takes."""
         pad = lambda n: -(-max(n, 1) // 4) * 4
         s = capacity.seqs
-        total = 3 * pad(s) + pad(s + 1) + 3 * pad(s)
+        total = 3 * pad(s) + pad(s + 1) + 4 * pad(s)
         total += n_groups * (pad(s * capacity.table_width) + pad(s))
         total += len(set(tile_sizes)) * 2 * pad(s)
         return total

@@ -5,35 +5,52 @@ entries or none: `OutOfBlocks` leaves the cache as it was), packs the batch with
 device, runs the model over exactly those tokens and counts them into the requests. Portions of
 prompts and single decoded tokens share a batch, cut anywhere. The reference runs one call per
 prefilling request and then one decode batch (layover/engine.py:156-189); here both are one
-batch.
+batch. `sample(entries)` does the same and then chooses a token for every wanted row on the
+device (`sampling.Sampler`), returning them on their way to the host.
 
-A step of single tokens only (every live request decoding) can replay a captured CUDA graph:
-one graph per batch size bucket, with the batch's descriptors at a fixed address and unused rows
-padded onto the scratch page (the reference captures batch 1, 2, 4, 8 the same way,
-layover/decode_graphs.py:25-100).
+A step of single tokens only (every live request decoding) can replay a captured CUDA graph: one
+graph per (batch size bucket, block-table width bucket), with the batch's descriptors at a fixed
+address and unused rows padded onto the scratch page and the scratch record (the reference
+captures batch 1, 2, 4, 8 the same way, layover/decode_graphs.py:25-100). The width bucket is the
+request's pages rounded up to a power of two, so the attention's split count is planned for about
+the context that is really there, not for the longest a request could ever get.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .. import ops
+from .. import ops, profiling
+from ..cache.allocator import OutOfBlocks
 from ..cache.manager import CacheManager
-from ..profiling import nvtx_range
-from .batch import BatchBuilder, BatchCapacity, StepEntry
+from ..sampling.sampler import PendingTokens, Sampler
+from .batch import DEVICE_TOKEN, BatchBuilder, BatchCapacity, StepEntry
 
 DEFAULT_GRAPH_SIZES = (1, 2, 4, 8, 16, 32, 64)
+MIN_GRAPH_WIDTH = 64          # pages: the smallest block-table bucket a graph is captured for
 
 
 class _DecodeGraph:
-    def __init__(self, size: int, step: "StepFunction"):
-        self.size = size
+    """One captured decode step: `size` rows, tables `width` pages wide, with or without sampling."""
+
+    def __init__(self, size: int, width: int, sampled: bool, step: "StepFunction"):
+        self.size, self.width, self.sampled = size, width, sampled
         cache = step.cache
-        self.capacity = BatchCapacity(size, step.graph_table_width)
+        self.capacity = BatchCapacity(size, width)
         words = BatchBuilder.buffer_size(self.capacity, len(cache.paged), step.builder.tile_sizes)
         self.buffer = torch.zeros(words, dtype=torch.int32, device=step.device)
+        self.tokens = None
+        if sampled:
+            self.tokens = torch.zeros(size + step.sampler.n_status, dtype=torch.int32, device=step.device)
         self.graph = None
         self.logits = None
+        self.launches = 0
+
+    def _run(self, step: "StepFunction", batch):
+        logits = step.model.forward(batch, step.cache)
+        if self.sampled:
+            step.sampler.sample_into(logits, batch, self.tokens)
+        return logits
 
     def capture(self, step: "StepFunction", pool):
         batch = step.builder.build([], self.capacity, self.buffer)   # padding rows only
@@ -41,50 +58,64 @@ class _DecodeGraph:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                step.model.forward(batch, step.cache)
+                self._run(step, batch)
         torch.cuda.current_stream().wait_stream(side)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
         with torch.cuda.graph(self.graph, pool=pool):
-            self.logits = step.model.forward(batch, step.cache)
+            self.logits = self._run(step, batch)
         self.launches = ops.LAUNCHES - before      # kernels one replay runs
         return self.graph.pool()
 
 
 class StepFunction:
     def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False,
-                 graph_sizes: tuple[int, ...] = DEFAULT_GRAPH_SIZES, graph_max_tokens: int | None = None):
+                 graph_sizes: tuple[int, ...] = DEFAULT_GRAPH_SIZES, graph_max_tokens: int | None = None,
+                 sampler: Sampler | None = None):
         self.model, self.cache = model, cache
         self.device = model.device
         self.builder = BatchBuilder(cache, self.device, model.tile_sizes())
         self.vocab_size = model.spec.vocab_size
         self.max_position = model.spec.max_position
         self.cuda_graphs = cuda_graphs
+        # False: a step that has a graph runs the graph's own fixed-size batch through the kernels
+        # launch by launch instead of replaying it (the same launches with the same arguments; what
+        # a replay must reproduce bit for bit, which tests and the benchmark check)
+        self.replay_graphs = True
         self.graph_sizes = tuple(sorted(s for s in graph_sizes if s <= cache.max_requests))
         limit = graph_max_tokens or self.max_position
         self.graph_table_width = max(1, min(cache.blocks_for(limit), max(cache.num_blocks, 1)))
-        self._graphs: dict[int, _DecodeGraph] = {}
+        if sampler is None:
+            sampler = Sampler(self.device, cache.records, model.kernel_libraries(model.dtype))
+        self.sampler = sampler
+        self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
         self._graph_pool = None
         self.steps = 0
         self.graph_replays = 0
         self.replayed_launches = 0
 
     # ---- checks the kernels cannot make
-    def _check(self, entries: list[StepEntry], previous_rows: int = 0) -> None:
+    def _check(self, entries: list[StepEntry]) -> None:
         seen = set()
+        live = self.cache.live
         for entry in entries:
             seq = entry.seq
-            if seq.closed:
-                raise ValueError(f"request {seq.request_id!r} is closed")
+            if seq.closed or live.get(seq.request_id) is not seq:
+                raise ValueError(f"request {seq.request_id!r} is closed or does not belong to this cache")
             if id(seq) in seen:
                 raise ValueError(f"request {seq.request_id!r} appears twice in one step")
             seen.add(id(seq))
             if not entry.tokens:
                 raise ValueError(f"request {seq.request_id!r}: no tokens in this step")
+            if not 0 <= seq.slot < self.cache.max_requests:
+                raise ValueError(f"request {seq.request_id!r}: state slot {seq.slot} is outside the cache")
             if seq.num_tokens + len(entry.tokens) > self.max_position:
                 raise ValueError(f"request {seq.request_id!r} would exceed {self.max_position} positions")
             for token in entry.tokens:
-                if not -previous_rows <= token < self.vocab_size:
+                if token == DEVICE_TOKEN:
+                    if len(entry.tokens) != 1:
+                        raise ValueError(f"request {seq.request_id!r}: a token still on the device comes alone")
+                elif not 0 <= token < self.vocab_size:
                     raise ValueError(f"request {seq.request_id!r}: token {token} is outside the vocabulary")
 
     def _reserve(self, entries: list[StepEntry]) -> None:
@@ -96,63 +127,91 @@ class StepFunction:
                 totals[g] += count
         for group, need in zip(cache.paged, totals):
             if need > group.allocator.num_free:
-                from ..cache.allocator import OutOfBlocks
                 raise OutOfBlocks(f"this step needs {need} blocks, {group.allocator.num_free} free")
         for entry in entries:
             cache.grow(entry.seq, entry.seq.num_tokens + len(entry.tokens))
 
     # ---- the step
-    def __call__(self, entries: list[StepEntry], previous_tokens: torch.Tensor | None = None) -> torch.Tensor:
+    def __call__(self, entries: list[StepEntry]) -> torch.Tensor:
         """Logits [wanted rows, vocab] in 32-bit on the device, in the order of entries and want.
 
-        `previous_tokens` (int32, on the device) are the tokens the step before sampled; entries name
-        them with negative token values, so a step can be launched before the host has read them.
         After a replayed graph the result is a view of the graph's output, which the next replay
-        of the same bucket overwrites: use it (sample, copy) before the next step."""
-        self._check(entries, 0 if previous_tokens is None else previous_tokens.shape[0])
+        of the same graph overwrites: use it (copy it) before the next step."""
+        return self._step(entries, sampled=False)
+
+    def sample(self, entries: list[StepEntry]) -> PendingTokens:
+        """The same step, then one token for every wanted row, chosen on the device as the requests'
+        records say; `result()` of what is returned waits for them (in the order of entries and want)."""
+        return self._step(entries, sampled=True)
+
+    def _step(self, entries: list[StepEntry], sampled: bool):
+        self._check(entries)
         self._reserve(entries)
-        with nvtx_range("step"):
-            graph = self._graph_for(entries)
+        with profiling.nvtx_range("step"):
+            graph = self._graph_for(entries, sampled)
             if graph is not None:
                 batch = self.builder.build(entries, graph.capacity, graph.buffer)
-                if batch.device_tokens:
-                    ops.patch_tokens(batch.token_ids, batch.token_src, previous_tokens)
-                graph.graph.replay()
-                self.graph_replays += 1
-                self.replayed_launches += graph.launches
+                if self.replay_graphs:
+                    graph.graph.replay()
+                    logits = graph.logits
+                    self.graph_replays += 1
+                    self.replayed_launches += graph.launches
+                else:
+                    logits = graph._run(self, batch)
                 rows = [i for i, e in enumerate(entries) if e.want]
-                logits = graph.logits[: len(entries)] if len(rows) == len(entries) else graph.logits[rows]
+                if sampled:
+                    if len(rows) != len(entries):
+                        raise ValueError("a replayed sampled step samples every row")     # _graph_for saw to it
+                    out = self.sampler.collect(graph.tokens, len(entries), graph.size)
+                else:
+                    out = logits[: len(entries)] if len(rows) == len(entries) else logits[rows]
             else:
                 batch = self.builder.build(entries)
-                if batch.device_tokens:
-                    ops.patch_tokens(batch.token_ids, batch.token_src, previous_tokens)
-                logits = self.model.forward(batch, self.cache)
+                out = self.model.forward(batch, self.cache)
+                if sampled:
+                    out = self.sampler.launch(out, batch)
         for entry in entries:
             self.cache.commit(entry.seq, entry.seq.num_tokens + len(entry.tokens))
         self.steps += 1
-        return logits
+        return out
 
-    def _graph_for(self, entries: list[StepEntry]) -> _DecodeGraph | None:
-        if not self.cuda_graphs or any(len(e.tokens) != 1 or e.want not in ([0], []) for e in entries):
+    def graph_width_for(self, pages: int) -> int | None:
+        """The block-table bucket for a longest request of `pages` pages; None: wider than any graph."""
+        if pages > self.graph_table_width:
+            return None
+        width = MIN_GRAPH_WIDTH
+        while width < pages:
+            width *= 2
+        return min(width, self.graph_table_width)
+
+    def _graph_for(self, entries: list[StepEntry], sampled: bool) -> _DecodeGraph | None:
+        if not self.cuda_graphs or any(len(e.tokens) != 1 for e in entries):
+            return None
+        if any(e.want != [0] for e in entries) if sampled else any(e.want not in ([0], []) for e in entries):
             return None
         size = next((s for s in self.graph_sizes if s >= len(entries)), None)
         if size is None:
             return None
-        if max(self.cache.blocks_for(e.seq.num_tokens + 1) for e in entries) > self.graph_table_width:
+        width = self.graph_width_for(max(self.cache.blocks_for(e.seq.num_tokens + 1) for e in entries))
+        if width is None:
             return None
-        graph = self._graphs.get(size)
+        graph = self._graphs.get((size, width, sampled))
         if graph is None:
-            graph = self._capture(size)
+            graph = self._capture(size, width, sampled)
         return graph
 
-    def _capture(self, size: int) -> _DecodeGraph:
-        graph = _DecodeGraph(size, self)
+    def _capture(self, size: int, width: int, sampled: bool) -> _DecodeGraph:
+        graph = _DecodeGraph(size, width, sampled, self)
         self._graph_pool = graph.capture(self, self._graph_pool)
-        self._graphs[size] = graph
+        self._graphs[(size, width, sampled)] = graph
         return graph
 
-    def capture_all(self) -> None:
-        """Capture every bucket now, largest first so that the smaller ones fit in its memory pool."""
+    def capture_all(self, tokens: int | None = None, sampled: bool = True) -> None:
+        """Capture every batch-size bucket now for requests of up to `tokens` tokens (default: the
+        widest table), largest first so that the smaller ones fit in its memory pool."""
+        width = self.graph_width_for(self.cache.blocks_for(tokens)) if tokens else self.graph_table_width
+        if width is None:
+            raise ValueError(f"{tokens} tokens are more than a captured step can hold")
         for size in reversed(self.graph_sizes):
-            if size not in self._graphs:
-                self._capture(size)
+            if (size, width, sampled) not in self._graphs:
+                self._capture(size, width, sampled)

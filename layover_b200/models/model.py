@@ -11,8 +11,8 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..parts.base import Runtime, build_part
-from ..profiling import nvtx_range
+from .. import profiling
+from ..parts.base import Runtime, build_part, walk_parts
 from ..weights.loader import TensorSpec
 from .spec import ModelSpec
 
@@ -25,7 +25,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, spec.norm_prefix)
         self.embedding = self.head = None
         self.runtime: Runtime | None = None
-        self._range_names = [(f"layer{e.layer}.attention", f"layer{e.layer}.mlp") for e in spec.schedule]
+        self._range_names = [f"layer{e.layer}" for e in spec.schedule]
 
     # ---- weights
     def tensor_specs(self) -> list[TensorSpec]:
@@ -59,7 +59,7 @@ class Model:
         """Bytes of every weight tensor a decode step reads once (the embedding counts only as the head)."""
         seen, total = set(), 0
         for block in self.blocks:
-            for part in block.parts():
+            for part in walk_parts(block):
                 for value in vars(part).values():
                     if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
                         seen.add(value.data_ptr())
@@ -73,18 +73,39 @@ class Model:
         return [(index, self.blocks[entry.layer].cache_need(), entry.reads_cache_of)
                 for index, entry in enumerate(self.spec.schedule)]
 
+    def all_parts(self):
+        """Every part of the model, the blocks' sub-parts included."""
+        for top in [*self.blocks, self.final_norm]:
+            yield from walk_parts(top)
+
+    def kernel_libraries(self, dtype: torch.dtype, runtime: Runtime | None = None) -> tuple[str, ...]:
+        """What has to be compiled before the first step of a run of `dtype`: the model's own kernels
+        (embedding, sampling), the run's matrix product and whatever the parts say they launch."""
+        runtime = runtime or self.runtime
+        names = ["elementwise", "sampling", *(runtime.kernel_libraries if runtime else ())]
+        for part in self.all_parts():
+            names += part.kernel_libraries(dtype)
+        return tuple(dict.fromkeys(names))
+
     def tile_sizes(self) -> tuple[int, ...]:
-        return self.runtime.tile_sizes
+        """Query-tile sizes that the parts want listed in every batch."""
+        sizes = [size for part in self.all_parts() for size in part.tile_sizes(self.runtime.dtype)]
+        return tuple(sorted(set(sizes)))
 
     # ---- one step
     def forward(self, batch, cache) -> torch.Tensor:
         rt = self.runtime
         batch.shared.clear()    # what parts share within a step (rotary tables) is made anew by every run
         x = torch.empty((batch.n_tokens, self.spec.hidden_size), dtype=rt.dtype, device=rt.device)
-        ops.embed(batch.token_ids, self.embedding, x)
+        records = getattr(cache, "records", None)      # tokens the host has not seen yet come from the requests' records
+        ops.embed(batch.token_ids, self.embedding, x, batch.token_src if records is not None else None, records)
         delta = None
-        for index, entry in enumerate(self.spec.schedule):
-            with nvtx_range(self._range_names[index][0]):
+        if profiling.active():
+            for index, entry in enumerate(self.spec.schedule):
+                with profiling.nvtx_range(self._range_names[index]):
+                    x, delta = self.blocks[entry.layer].forward(x, delta, batch, cache.view(index))
+        else:
+            for index, entry in enumerate(self.spec.schedule):
                 x, delta = self.blocks[entry.layer].forward(x, delta, batch, cache.view(index))
         if batch.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)

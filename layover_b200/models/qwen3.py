@@ -16,12 +16,15 @@ def qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
     def norm(weight: str, dim: int) -> PartSpec:
         return PartSpec("rmsnorm", {"dim": dim, "eps": cfg.rms_norm_eps, "weight": weight})
 
+    attention_names = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
+                       "o": "self_attn.o_proj.weight", "q_norm": "self_attn.q_norm.weight",
+                       "k_norm": "self_attn.k_norm.weight"}
     layers = []
     for index in range(cfg.num_hidden_layers):
         block = PartSpec("pre_norm", {
             "input_norm": norm("input_layernorm.weight", cfg.hidden_size),
             "mixer": attention_spec(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                                    qk_norm_eps=cfg.rms_norm_eps, theta=cfg.rope_theta),
+                                    qk_norm_eps=cfg.rms_norm_eps, theta=cfg.rope_theta, names=attention_names),
             "post_norm": norm("post_attention_layernorm.weight", cfg.hidden_size),
             "feed_forward": PartSpec("gated_mlp", {
                 "hidden": cfg.hidden_size, "inter": cfg.intermediate_size, "activation": "silu",

@@ -78,20 +78,25 @@ def _fn(lib_name: str, fn_name: str, argtypes):
 
 
 # ------------------------------------------------------------------ elementwise
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = table[ids[t]]; ids int32 [T], table [V, H], out [T, H]."""
+RECORD_WORDS = 8                 # int32 words of a request's record on the device (csrc/common.cuh)
+RECORD_POSITION, RECORD_SEED_LO, RECORD_SEED_HI, RECORD_COUNT, RECORD_TEMPERATURE, RECORD_LAST_TOKEN = range(6)
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, token_src: torch.Tensor | None = None,
+          records: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[id]; ids int32 [T], table [V, H], out [T, H]. Where token_src[t] >= 0 the id is the
+    last token in row token_src[t] of `records` (int32 [slots, RECORD_WORDS]) instead of ids[t]."""
     _need(ids, torch.int32, "ids"); _need(table, None, "table"); _need(out, table.dtype, "out")
-    fn = _fn("elementwise", "lb_embed", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(dtype_code(table.dtype), _ptr(ids), _ptr(table), _ptr(out), ids.shape[0], table.shape[1], _stream()),
-           "embed")
+    if (token_src is None) != (records is None):
+        raise ValueError("embed: token_src and records come together")
+    if token_src is not None:
+        _need(token_src, torch.int32, "token_src"); _need(records, torch.int32, "records")
+        if records.dim() != 2 or records.shape[1] != RECORD_WORDS or token_src.shape[0] != ids.shape[0]:
+            raise ValueError("embed: records must be [slots, RECORD_WORDS] and token_src one entry per token")
+    fn = _fn("elementwise", "lb_embed", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(table.dtype), _ptr(ids), _ptr(token_src), _ptr(records), _ptr(table), _ptr(out), ids.shape[0],
+              table.shape[1], table.shape[0], _stream()), "embed")
     return out
-
-
-def patch_tokens(ids: torch.Tensor, source: torch.Tensor, previous: torch.Tensor) -> None:
-    """ids[t] = previous[source[t]] where source[t] >= 0 (tokens sampled by a step the host has not read yet)."""
-    _need(ids, torch.int32, "ids"); _need(source, torch.int32, "source"); _need(previous, torch.int32, "previous")
-    fn = _fn("elementwise", "lb_patch_tokens", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
-    _check(fn(_ptr(ids), _ptr(source), _ptr(previous), ids.shape[0], _stream()), "patch_tokens")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -214,30 +219,108 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     return out
 
 
-# ------------------------------------------------------------------ sampling
-def sample(logits: torch.Tensor, temperature: torch.Tensor | None, seed_lo: torch.Tensor | None,
-           seed_hi: torch.Tensor | None, step: torch.Tensor | None, tokens: torch.Tensor) -> torch.Tensor:
-    """tokens[r] = argmax(logits[r]) for temperature 0, else a Gumbel-max draw at that temperature.
+def attention_f32(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):
+    """The 32-bit path's attention for one step: one kernel for every mix of segment lengths."""
+    tiles = batch.tiles[attention_simt_block_queries()]
+    attention_simt(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
+                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window)
 
-    logits float32 [R, V] (rows may be strided); temperature float32 [R]; seed_lo, seed_hi, step int32 [R]
-    (read as unsigned); tokens int32 [R]. With temperature None every row is greedy."""
+
+# ------------------------------------------------------------------ sampling
+def sample(logits: torch.Tensor, tokens: torch.Tensor, records: torch.Tensor | None = None,
+           row_slots: torch.Tensor | None = None, positions: torch.Tensor | None = None,
+           logit_rows: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """tokens[r] = the next token of row r of logits (float32 [R, V], rows may be strided).
+
+    With `records` (int32 [slots, RECORD_WORDS]) and `row_slots` (int32 [R]) row r belongs to the
+    request in slot row_slots[r]: temperature 0 there is the first index of the maximum, otherwise a
+    Gumbel-max draw keyed by the record's seed and counter; the kernel stores the token as the
+    record's last token, bumps its counter and, given `positions` [T] and `logit_rows` [R], sets its
+    position. Without records every row is greedy. `status` (int64 device addresses of other
+    libraries' error words, from `status_words`) are copied to tokens[R:], so tokens holds
+    R + len(status) ints."""
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("sample: logits must be float32 [rows, vocab] with a contiguous vocabulary")
     _need(tokens, torch.int32, "tokens")
     rows, vocab = logits.shape
-    if temperature is not None:
-        _need(temperature, torch.float32, "temperature")
-        for name, t in (("seed_lo", seed_lo), ("seed_hi", seed_hi), ("step", step)):
+    n_status = 0 if status is None else status.shape[0]
+    if tokens.shape[0] < rows + n_status:
+        raise ValueError("sample: tokens must hold a word per row and per status word")
+    if records is not None:
+        _need(records, torch.int32, "records"); _need(row_slots, torch.int32, "row_slots")
+        if records.dim() != 2 or records.shape[1] != RECORD_WORDS or row_slots.shape[0] < rows:
+            raise ValueError("sample: records must be [slots, RECORD_WORDS] and row_slots one entry per row")
+    for name, t in (("positions", positions), ("logit_rows", logit_rows)):
+        if t is not None:
             _need(t, torch.int32, name)
-    fn = _fn("sampling", "lb_sample", [c_void_p, c_long, c_int, c_int] + [c_void_p] * 6)
-    _check(fn(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed_lo), _ptr(seed_hi),
-              _ptr(step), _ptr(tokens), _stream()), "sample")
+    if status is not None:
+        _need(status, torch.int64, "status")
+    fn = _fn("sampling", "lb_sample", [c_void_p, c_long, c_int, c_int] + [c_void_p] * 6 + [c_int, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), rows, vocab, _ptr(records), _ptr(row_slots), _ptr(positions),
+              _ptr(logit_rows), _ptr(tokens), _ptr(status), n_status, _stream()), "sample")
     return tokens
 
 
-# ------------------------------------------------------------------ the bfloat16 path
-BF16_LIBRARIES = ("elementwise", "gemm_simt", "gemm_tcgen05", "attention_mma", "attention_tcgen05", "sampling")
+# ------------------------------------------------------------------ error words of the tensor-core kernels
+# Every wait inside the tcgen05 kernels is bounded; a wait that runs out records a code in the
+# library's error word and the block leaves. The sampling kernel copies those words behind the
+# tokens it writes, so the host sees them with every step's tokens and without a synchronisation
+# of its own (`Sampler`); `status_words` lists them, `explain_status` names a code's library, and
+# `reset_after_error` puts back what such a block may have left behind (counters that a launch
+# normally returns to zero).
+_STATUS_LIBRARIES = (("gemm_tcgen05", "lb_gemm_tcgen05_status_address", "lb_gemm_tcgen05_status"),
+                     ("attention_tcgen05", "lb_attention_tcgen05_status_address", "lb_attention_tcgen05_status"))
+_status_words: dict[tuple[int, tuple[str, ...]], tuple[torch.Tensor, tuple[str, ...]]] = {}
 
+
+def status_words(device: torch.device, libraries) -> tuple[torch.Tensor | None, tuple[str, ...]]:
+    """(int64 device tensor of the error words' addresses, the libraries they belong to) for those of
+    `libraries` that have one; (None, ()) if none has."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    wanted = tuple(name for name, _, _ in _STATUS_LIBRARIES if name in libraries)
+    key = (index, wanted)
+    if key not in _status_words:
+        addresses = []
+        with torch.cuda.device(index):
+            for name, getter, _ in _STATUS_LIBRARIES:
+                if name in wanted:
+                    fn = getattr(build.load(name), getter)
+                    fn.restype = c_void_p
+                    address = fn()
+                    if not address:
+                        raise KernelError(f"{name}: the address of its error word cannot be had")
+                    addresses.append(address)
+            tensor = torch.tensor(addresses, dtype=torch.int64, device="cuda") if addresses else None
+        _status_words[key] = (tensor, wanted)
+    return _status_words[key]
+
+
+def reset_after_error(device: torch.device) -> None:
+    """After a kernel reported a wait that ran out: wait for the device, clear the error words and zero
+    the split counters (a block that gave up does not take part in returning them to zero)."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    with torch.cuda.device(index):
+        torch.cuda.synchronize()
+        for name, _, clear in _STATUS_LIBRARIES:
+            if name in build.loaded():
+                fn = getattr(build.load(name), clear)
+                fn.restype = c_int
+                fn()
+        if index in _scratch:
+            _scratch[index][1].zero_()
+        if index in _attn_scratch:
+            _attn_scratch[index][1].zero_()
+        torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------ the bfloat16 path
+# Split-K scratch and counters are one set per device, shared by every model, engine and stream of
+# the process: a launch leaves its counters at zero for the next one, and two launches that overlap
+# on the device would mix their partial tiles. So all launches of a device must be ordered on ONE
+# stream (the engine runs everything on torch's current stream; the warm-up of a graph capture runs
+# on a side stream only while the main stream waits for it).
 _SCRATCH_FLOATS = 8 << 20     # split-K partial tiles (32 MiB)
 _SCRATCH_COUNTERS = 4096
 _scratch: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = {}
@@ -443,8 +526,13 @@ TCGEN05_TILE = 128
 _pool_maps: dict[tuple, object] = {}
 
 
+def attention_tcgen05_takes_heads(q_heads: int, kv_heads: int, dim: int) -> bool:
+    """Whether the tcgen05 prompt attention has a kernel for these heads (whatever the page size)."""
+    return dim == 128 and kv_heads > 0 and q_heads % kv_heads == 0 and q_heads // kv_heads <= 128
+
+
 def attention_tcgen05_supports(q_heads: int, kv_heads: int, dim: int, page_tokens: int) -> bool:
-    return (dim == 128 and kv_heads > 0 and q_heads % kv_heads == 0 and q_heads // kv_heads <= 128
+    return (attention_tcgen05_takes_heads(q_heads, kv_heads, dim)
             and page_tokens >= 8 and page_tokens % 8 == 0 and 128 % page_tokens == 0)
 
 
@@ -487,10 +575,6 @@ def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, t
               block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads, kv_heads,
               dim, page_tokens, float(scale), int(window), _stream()), "attention_tcgen05_prefill")
     return out
-
-
-def attention_bf16_tile_sizes() -> tuple[int, ...]:
-    return (attention_mma_block_queries(), TCGEN05_TILE)
 
 
 def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window):

@@ -20,7 +20,14 @@ class Attention(Part):
     params: hidden, q_heads, kv_heads, head_dim; qk_norm_eps (None: no per-head norm);
     position (a PartSpec or None); window (None: every earlier key is seen);
     shares_cache (True: the layer has no k/v projections and attends over another layer's
-    pages); tensor names q, k, v, o, q_norm, k_norm relative to the prefix.
+    pages); tensor names q, k, v, o (and q_norm, k_norm with a per-head norm) relative to the
+    prefix: the architecture's spec gives them, the part knows no checkpoint's naming.
+
+    Kernels are chosen when the part is bound: a float32 run attends with the one 32-bit kernel
+    for every segment length; a bfloat16 run with the tensor-core kernels (tcgen05 tiles where
+    they take the head size, mma.sync tiles elsewhere, the split decode kernel for single
+    tokens) and, for steps of few tokens, a q/k/v product with norm, rotation and page write in
+    its epilogue.
 
     The three projections are stacked at load into one [(q_heads + 2 kv_heads) head_dim, hidden]
     matrix (the reference runs three products, layover/model.py:121-123)."""
@@ -41,11 +48,13 @@ class Attention(Part):
         self.shares_cache = bool(p.get("shares_cache", False))
         self.scale = float(p.get("scale", 1.0 / math.sqrt(self.dim)))
         self.position = build_part("position", p.get("position"), prefix)
-        names = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
-                 "o": "self_attn.o_proj.weight", "q_norm": "self_attn.q_norm.weight",
-                 "k_norm": "self_attn.k_norm.weight"}
-        self.names = {k: prefix + p.get(k, default) for k, default in names.items()}
+        wanted = ["q", "o"] + ([] if self.shares_cache else ["k", "v"])
+        if self.qk_norm_eps is not None:
+            wanted += ["q_norm"] + ([] if self.shares_cache else ["k_norm"])
+        self.require(*wanted)
+        self.names = {k: prefix + p[k] for k in wanted}
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        self._attend = self._project_heads = None
 
     # ---- what it wants
     def tensor_specs(self):
@@ -66,8 +75,32 @@ class Attention(Part):
     def cache_need(self):
         return PagedKVNeed(self.kv_heads, self.dim, self.window)
 
+    def parts(self):
+        return [self.position] if self.position is not None else []
+
+    def kernel_libraries(self, dtype):
+        if dtype == torch.float32:
+            return ("elementwise", "attention_simt")
+        names = ["elementwise", "attention_mma"]
+        if ops.attention_tcgen05_takes_heads(self.q_heads, self.kv_heads, self.dim):
+            names.append("attention_tcgen05")
+        return tuple(names)
+
+    def tile_sizes(self, dtype):
+        if dtype == torch.float32:
+            return (ops.attention_simt_block_queries(),)
+        sizes = [ops.attention_mma_block_queries()]
+        if ops.attention_tcgen05_takes_heads(self.q_heads, self.kv_heads, self.dim):
+            sizes.append(ops.TCGEN05_TILE)
+        return tuple(sizes)
+
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
+        if runtime.dtype == torch.float32:
+            self._attend, self._project_heads = ops.attention_f32, None
+        else:
+            ops.attention_scratch(runtime.device)      # made now, never inside a graph capture
+            self._attend, self._project_heads = ops.attention_bf16, ops.gemm_qkv_heads
         n = self.names
         if self.shares_cache:
             self.w_qkv = tensors[n["q"]]
@@ -90,7 +123,7 @@ class Attention(Part):
         table = self.position.tables(batch) if self.position is not None else None
         fused = self.position is None or table is not None
         k_pool, v_pool = (cache.k_pool, cache.v_pool) if own_kv else (None, None)
-        heads = self.runtime.linear_heads
+        heads = self._project_heads
         if (heads is not None and own_kv and table is not None and self.qk_norm_eps is not None
                 and heads(h, self.w_qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, group.slot_map,
                           self.q_heads, own_kv, self.dim, cache.page_tokens, eps)):
@@ -116,13 +149,15 @@ class Attention(Part):
         return self.runtime.linear(out, self.w_o)
 
     def attend(self, q, cache, batch, group, out) -> None:
-        self.runtime.attention(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim,
-                               cache.page_tokens, self.scale, self.window or 0)
+        self._attend(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim,
+                     cache.page_tokens, self.scale, self.window or 0)
 
 
-def attention_spec(hidden, q_heads, kv_heads, head_dim, qk_norm_eps, theta, window=None, shares_cache=False) -> PartSpec:
+def attention_spec(hidden, q_heads, kv_heads, head_dim, qk_norm_eps, theta, names: dict[str, str], window=None,
+                   shares_cache=False) -> PartSpec:
+    """`names`: the checkpoint's tensor names for q, k, v, o, q_norm, k_norm, relative to the layer's prefix."""
     position = PartSpec("rotary_half", {"dim": head_dim, "theta": theta}) if theta is not None else None
     return PartSpec("attention", {
         "hidden": hidden, "q_heads": q_heads, "kv_heads": kv_heads, "head_dim": head_dim,
-        "qk_norm_eps": qk_norm_eps, "position": position, "window": window, "shares_cache": shares_cache,
+        "qk_norm_eps": qk_norm_eps, "position": position, "window": window, "shares_cache": shares_cache, **names,
     })

@@ -9,7 +9,11 @@ model spec of an architecture then names it, layer by layer.
 What each kind must offer:
 
   every part      tensor_specs() -> [TensorSpec]      the checkpoint tensors it wants
-                  bind(tensors, runtime)              take them (fuse or reshape as it likes)
+                  bind(tensors, runtime)              take them (fuse or reshape as it likes) and choose
+                                                      its kernels for runtime.dtype
+                  parts() -> [Part]                   its own sub-parts (default: none)
+                  kernel_libraries(dtype) -> names    kernel libraries it launches (default: none)
+                  tile_sizes(dtype) -> sizes          query-tile lists it wants in a batch (default: none)
   norm            forward(x, delta, rows=None) -> h   x += delta in place (delta may be None), h = norm(x);
                                                       with rows, only those rows, x untouched
   position        tables(batch) -> float32 [T, 2, dim/2] cos/sin of the step, or None; made once per
@@ -48,6 +52,10 @@ class PagedKVNeed:
     head_dim: int
     window: int | None = None
 
+    def elements_per_token(self) -> int:
+        """Pool elements one token takes in one layer with this need (keys and values)."""
+        return 2 * self.kv_heads * self.head_dim
+
 
 @dataclass(frozen=True)
 class StateNeed:
@@ -58,22 +66,15 @@ class StateNeed:
 
 @dataclass
 class Runtime:
-    """What a part needs to know about the run: precision, device and the matrix product."""
+    """What a part needs to know about the run: its precision, its device and the matrix product
+    of that precision. Everything else (which attention kernel, which fused product) a part
+    chooses for itself from `dtype` when it is bound; `extras` carries whatever else a caller
+    wants its own parts to find (the package's parts read nothing from it)."""
     dtype: torch.dtype
     device: torch.device
     linear: Callable[..., torch.Tensor]   # linear(a [M, K], w [N, K], out_dtype=None) -> [M, N]
-    # attention(q, cache_view, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window)
-    attention: Callable[..., None] | None = None
-    # linear_swiglu(a, w_interleaved) -> silu(gate) * up or None; w made by interleave_gate_up(gate, up)
-    linear_swiglu: Callable[..., torch.Tensor | None] | None = None
-    interleave_gate_up: Callable[..., torch.Tensor] | None = None
-    # linear_heads(h, w_qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, table, slot_map, q_heads, kv_heads, dim,
-    #              page_tokens, eps) -> bool: the stacked q/k/v projection with the per-head norm, the rotation
-    #              and the page write in its epilogue; False (nothing done) where the run or the sizes have none
-    linear_heads: Callable[..., bool] | None = None
-    swiglu_block: int = 0                 # the fused product wants the width to be a multiple of this
-    tile_sizes: tuple[int, ...] = ()      # query-tile sizes whose tile lists the batch must carry
-    kernel_libraries: tuple[str, ...] = ()  # what has to be compiled before the first step
+    kernel_libraries: tuple[str, ...] = ()  # what `linear` itself needs compiled
+    extras: dict = field(default_factory=dict)
 
 
 class Part:
@@ -87,10 +88,33 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
 
+    def parts(self) -> list["Part"]:
+        """The parts this one is made of (a block's norms, mixer and feed-forward; a mixer's
+        position encoding), so that a model can ask all of them what they need."""
+        return []
+
+    def kernel_libraries(self, dtype: torch.dtype) -> tuple[str, ...]:
+        """Names of the kernel libraries this part launches in a run of `dtype`: the package's own
+        (`csrc/build.py`'s SOURCES) or sources registered with `csrc.build.register_source`. They are
+        compiled before the model's first step."""
+        return ()
+
+    def tile_sizes(self, dtype: torch.dtype) -> tuple[int, ...]:
+        """Query-tile sizes whose (sequence, first query) lists every step's batch must carry."""
+        return ()
+
     def require(self, *names: str) -> None:
         missing = [n for n in names if n not in self.params]
         if missing:
             raise ValueError(f"{type(self).__name__} lacks parameters {missing}")
+
+
+def walk_parts(part: "Part"):
+    """`part` and everything below it, depth first."""
+    yield part
+    for child in part.parts():
+        if child is not None:
+            yield from walk_parts(child)
 
 
 _REGISTRIES: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}}

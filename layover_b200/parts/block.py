@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+from .. import profiling
 from .base import Part, build_part, register_block
 
 
@@ -38,6 +39,13 @@ class PreNormBlock(Part):
         return self.mixer.cache_need()
 
     def forward(self, x, delta, batch, cache):
+        if profiling.active():
+            with profiling.nvtx_range("mixer"):
+                h = self.input_norm.forward(x, delta)
+                attended = self.mixer.forward(h, batch, cache)
+            with profiling.nvtx_range("feed_forward"):
+                h = self.post_norm.forward(x, attended)
+                return x, self.feed_forward.forward(h)
         h = self.input_norm.forward(x, delta)
         attended = self.mixer.forward(h, batch, cache)
         h = self.post_norm.forward(x, attended)

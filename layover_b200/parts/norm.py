@@ -31,6 +31,9 @@ class RMSNorm(Part):
         super().bind(tensors, runtime)
         self.weight = tensors[self.weight_name]
 
+    def kernel_libraries(self, dtype):
+        return ("elementwise",)
+
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.dim), dtype=x.dtype, device=x.device)

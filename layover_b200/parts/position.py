@@ -34,6 +34,9 @@ class RotaryHalf(Part):
         exponent = torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim
         self._table = (1.0 / (self.theta ** exponent)).to(runtime.device).contiguous()
 
+    def kernel_libraries(self, dtype):
+        return ("elementwise",)
+
     def inv_freq(self) -> torch.Tensor:
         return self._table
 

@@ -10,6 +10,8 @@ runs the entries of a step as ONE batch through the engine's own step function (
 cache manager and kernels that generation uses; nothing is sampled), writes `<out>/<step>.f32`
 (little-endian float32 [wanted, vocab], in the order of the entries and of `want`) when anything
 is wanted, gives back what the requests named in `end` hold, and prints `done <step>`.
+`--cuda-graphs` lets steps of single tokens replay captured graphs (padded to a bucket of
+requests), the way the serving engine runs them.
 `--max-tokens` sizes the page pool: the most tokens that live requests hold at any time, each
 request's count rounded up to a multiple of 64; pages are reused as requests end.
 
@@ -35,6 +37,8 @@ def parse_args(argv=None):
                         help="most tokens live requests hold at a time (each rounded up to 64)")
     parser.add_argument("--block-tokens", type=int, default=16, help="tokens per page (must divide 64)")
     parser.add_argument("--max-requests", type=int, default=16, help="most requests live at a time")
+    parser.add_argument("--cuda-graphs", action="store_true",
+                        help="replay steps of single tokens from captured CUDA graphs, as serving does")
     return parser.parse_args(argv)
 
 
@@ -52,7 +56,7 @@ def run(args, lines, say=print) -> int:
     model = load_model(args.model, device="cuda", dtype=args.dtype)
     pages = max(1, -(-args.max_tokens // args.block_tokens))
     cache = PagedKVCache(model, pages, block_tokens=args.block_tokens, max_requests=args.max_requests)
-    step_fn = StepFunction(model, cache)
+    step_fn = StepFunction(model, cache, cuda_graphs=getattr(args, "cuda_graphs", False))
     live = {}
     for line in lines:
         line = line.strip()

@@ -8,8 +8,9 @@ layover/weights.py:38-41). How a tensor is kept:
 
   "matrix"  an operand of a matrix product: the run's dtype (bfloat16 for serving, float32 for
             the true 32-bit path); floating tensors are cast once at load (layover/weights.py:35)
-  "vector"  a small per-channel parameter (norm weights): always float32 on the device, which
-            holds any stored bfloat16 value exactly
+  "vector"  a small per-channel parameter (norm weights): rounded to the run's dtype like every
+            floating tensor (layover/weights.py:35 casts them all), then kept as float32 on the
+            device, which holds any bfloat16 value exactly and is what the kernels read
   "keep32"  a tensor that must stay in 32-bit whatever the run's dtype is
   "int"     an integer table: int32
 """
@@ -110,5 +111,7 @@ def load_tensors(folder: str | Path, specs: list[TensorSpec], run_dtype: torch.d
             raise CheckpointMismatch(f"checkpoint mismatch: {spec.name} must be an integer table, is {host.dtype}")
         if spec.kind != "int" and not host.is_floating_point():
             raise CheckpointMismatch(f"checkpoint mismatch: {spec.name} must be floating point, is {host.dtype}")
+        if spec.kind == "vector":
+            host = host.to(run_dtype)       # the value the reference's cast leaves, whatever the file stores
         out[spec.name] = host.to(device=device, dtype=target_dtype(spec, host.dtype, run_dtype)).contiguous()
     return out

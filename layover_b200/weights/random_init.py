@@ -44,6 +44,8 @@ def random_tensors(specs: list[TensorSpec], seed: int, run_dtype: torch.dtype, d
     out = {}
     for spec in specs:
         t = random_tensor(spec, seed, std, norm_std, device)
+        if spec.kind == "vector":
+            t = t.to(run_dtype)             # rounded as a loaded checkpoint's would be
         out[spec.name] = t.to(target_dtype(spec, t.dtype, run_dtype)).contiguous()
     return out
 

@@ -74,6 +74,32 @@ def mixed(requests: dict[str, list[int]], live_limit: int = 4, prompt_part: floa
     return number(steps)
 
 
+def crowd(requests: dict[str, list[int]], decoded: int = 6, prompts_per_step: int = 16) -> list[dict]:
+    """Many requests at once: the prompts (all but the last `decoded` tokens of each) go in, several
+    whole prompts a step, then ALL requests decode together, one token each a step. Requests whose
+    tokens run out drop out of the later steps, so the number of rows also takes values that are no
+    bucket size."""
+    names = list(requests)
+    steps = []
+    for at in range(0, len(names), prompts_per_step):
+        entries = []
+        for name in names[at:at + prompts_per_step]:
+            head = max(1, len(requests[name]) - decoded)
+            entries.append({"id": name, "tokens": requests[name][:head], "want": list(range(head))})
+        steps.append({"entries": entries, "end": []})
+    done = {name: max(1, len(requests[name]) - decoded) for name in names}
+    while any(done[name] < len(requests[name]) for name in names):
+        entries, ended = [], []
+        for name in names:
+            if done[name] < len(requests[name]):
+                entries.append({"id": name, "tokens": [requests[name][done[name]]], "want": [0]})
+                done[name] += 1
+                if done[name] == len(requests[name]):
+                    ended.append(name)
+        steps.append({"entries": entries, "end": ended})
+    return number(steps)
+
+
 def number(steps: list[dict]) -> list[dict]:
     for index, step in enumerate(steps):
         step["step"] = index
@@ -93,11 +119,13 @@ def max_live_tokens(steps: list[dict], round_to: int = 64) -> int:
     return most
 
 
-def run_trace(folder, dtype: str, steps: list[dict], out: Path, max_tokens: int | None = None, block_tokens: int = 16):
+def run_trace(folder, dtype: str, steps: list[dict], out: Path, max_tokens: int | None = None, block_tokens: int = 16,
+              cuda_graphs: bool = False, max_requests: int = 8):
     """Feed `steps` through the replay program's own loop; returns {request: {position: logits row}}."""
     from layover_b200.replay.trace import run
 
-    args = SimpleNamespace(model=str(folder), dtype=dtype, out=str(out), block_tokens=block_tokens, max_requests=8,
+    args = SimpleNamespace(model=str(folder), dtype=dtype, out=str(out), block_tokens=block_tokens,
+                           max_requests=max_requests, cuda_graphs=cuda_graphs,
                            max_tokens=max_tokens if max_tokens is not None else max_live_tokens(steps))
     said = []
     assert run(args, [json.dumps(s) for s in steps], say=lambda text, flush=True: said.append(text)) == 0

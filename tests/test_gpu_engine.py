@@ -467,7 +467,9 @@ def test_a_toy_position_encoding_and_a_toy_routed_feed_forward_run_in_the_same_b
             layers.append(LayerSpec(PartSpec("pre_norm", {
                 "input_norm": norm("n1.weight"),
                 "mixer": PartSpec("attention", {"hidden": hidden, "q_heads": raw["q_heads"], "kv_heads": raw["kv_heads"],
-                                                "head_dim": raw["head_dim"], "qk_norm_eps": None, "position": position}),
+                                                "head_dim": raw["head_dim"], "qk_norm_eps": None, "position": position,
+                                                "q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight",
+                                                "v": "self_attn.v_proj.weight", "o": "self_attn.o_proj.weight"}),
                 "post_norm": norm("n2.weight"),
                 "feed_forward": PartSpec("routed", {"hidden": hidden, "inter": raw["inter"], "experts": 3})}), f"blocks.{i}."))
         return ModelSpec("ToyRoutedForCausalLM", raw["vocab_size"], hidden, 4096, "tok.weight", norm("final.weight"), None, layers)

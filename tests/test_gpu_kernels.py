@@ -287,6 +287,16 @@ def test_refused_sizes_raise_instead_of_computing():
         o.embed(torch.zeros(2, dtype=torch.int32), torch.zeros(3, 4), torch.zeros(2, 4))
 
 
+def make_records(o, temperatures, seeds, counts, slots_total=None):
+    """Per-request records as the cache manager holds them, one row per request (row r = slot r)."""
+    from layover_b200.sampling.sampler import SamplingParams, request_record
+    rows = [request_record(SamplingParams(float(t), int(s))) for t, s in zip(temperatures, seeds)]
+    records = torch.zeros((slots_total or len(rows), o.RECORD_WORDS), dtype=torch.int64)
+    records[: len(rows)] = torch.tensor(rows, dtype=torch.int64)
+    records[: len(rows), o.RECORD_COUNT] = torch.tensor([c - (1 << 32) if c >= (1 << 31) else c for c in counts])
+    return records.to(torch.int32).cuda()
+
+
 @pytest.mark.parametrize("vocab", [7, 512, 151936, 1000])
 def test_sampling_matches_the_plain_rule(vocab):
     o = ops()
@@ -295,20 +305,63 @@ def test_sampling_matches_the_plain_rule(vocab):
     logits = torch.randn(rows, vocab, generator=gen) * 3
     logits[0, vocab // 2] = logits[0].max() + 1          # a clear maximum
     logits[1, 3] = logits[1, 5] = logits[1].max() + 2    # equal maxima: the first wins
-    temperature = torch.tensor([0.0, 0.0, 0.8, 1.5, 0.8, 0.3])
+    temperature = [0.0, 0.0, 0.8, 1.5, 0.8, 0.3]
     seeds = [0, 0, 1234, 0xFFFFFFFF12345678, 1234, 99]
     steps = [0, 0, 0, 7, 1, 4000000000]
-    lo = torch.tensor([s & 0xFFFFFFFF for s in seeds], dtype=torch.int64).to(torch.int32)
-    hi = torch.tensor([(s >> 32) & 0xFFFFFFFF for s in seeds], dtype=torch.int64).to(torch.int32)
-    st = torch.tensor(steps, dtype=torch.int64).to(torch.int32)
-    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
-    o.sample(logits.cuda(), temperature.cuda(), lo.cuda(), hi.cuda(), st.cuda(), tokens)
-    expected = [plain_sample(logits[r].numpy(), float(temperature[r]), seeds[r], steps[r]) for r in range(rows)]
+    # the rows' requests sit in slots 5, 4, .. 0 of a pool of 9: the kernel must go through row_slots
+    records = make_records(o, temperature[::-1], seeds[::-1], steps[::-1], slots_total=9)
+    before = records.clone()
+    row_slots = torch.tensor([5, 4, 3, 2, 1, 0], dtype=torch.int32, device="cuda")
+    positions = torch.arange(40, 52, dtype=torch.int32, device="cuda")
+    logit_rows = torch.tensor([1, 3, 5, 7, 9, 11], dtype=torch.int32, device="cuda")
+    tokens = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+    o.sample(logits.cuda(), tokens, records, row_slots, positions, logit_rows)
+    expected = [plain_sample(logits[r].numpy(), temperature[r], seeds[r], steps[r]) for r in range(rows)]
     assert tokens.tolist() == expected
     assert expected[0] == vocab // 2 and expected[1] == 3
+    # what the kernel leaves in the records: the token, the counter one further, the position; nothing else
+    after = records.cpu().to(torch.int64)
+    for r in range(rows):
+        slot = 5 - r
+        assert after[slot, o.RECORD_LAST_TOKEN] == expected[r]
+        assert (after[slot, o.RECORD_COUNT] & 0xFFFFFFFF) == (steps[r] + 1) & 0xFFFFFFFF
+        assert after[slot, o.RECORD_POSITION] == 40 + 2 * r + 1 + 2
+    untouched = [o.RECORD_SEED_LO, o.RECORD_SEED_HI, o.RECORD_TEMPERATURE, 6, 7]
+    assert torch.equal(after[:, untouched], before.cpu().to(torch.int64)[:, untouched])
+    assert torch.equal(after[6:], before.cpu().to(torch.int64)[6:])
     greedy = torch.empty(rows, dtype=torch.int32, device="cuda")
-    o.sample(logits.cuda(), None, None, None, None, greedy)
+    o.sample(logits.cuda(), greedy)
     assert greedy.tolist() == logits.argmax(-1).tolist()
+
+
+def test_sampling_carries_other_kernels_error_words_behind_the_tokens():
+    o = ops()
+    words = torch.tensor([0, 5], dtype=torch.int32, device="cuda")        # stand-ins for two libraries' error words
+    status = torch.tensor([words.data_ptr(), words.data_ptr() + 4], dtype=torch.int64, device="cuda")
+    logits = torch.randn(3, 40, device="cuda")
+    tokens = torch.full((5,), -1, dtype=torch.int32, device="cuda")
+    o.sample(logits, tokens, status=status)
+    assert tokens.tolist() == logits.argmax(-1).tolist() + [0, 5]
+    with pytest.raises(ValueError, match="tokens must hold"):
+        o.sample(logits, torch.empty(3, dtype=torch.int32, device="cuda"), status=status)
+
+
+def test_embedding_takes_tokens_from_the_requests_records():
+    o = ops()
+    table = torch.randn(50, 24, device="cuda").to(torch.bfloat16)
+    records = make_records(o, [0.0] * 4, [0] * 4, [0] * 4)
+    records[:, o.RECORD_LAST_TOKEN] = torch.tensor([7, 49, 0, 12], dtype=torch.int32, device="cuda")
+    ids = torch.tensor([3, 0, 0, 9, 0], dtype=torch.int32, device="cuda")
+    source = torch.tensor([-1, 1, 3, -1, 0], dtype=torch.int32, device="cuda")
+    out = torch.empty(5, 24, dtype=torch.bfloat16, device="cuda")
+    o.embed(ids, table, out, source, records)
+    assert torch.equal(out, table[torch.tensor([3, 49, 12, 9, 7], device="cuda")])
+    o.embed(ids, table, out)
+    assert torch.equal(out, table[ids.long()])
+    odd = torch.randn(50, 23, device="cuda")                                  # rows that are no multiple of 16 bytes
+    out = torch.empty(5, 23, device="cuda")
+    o.embed(ids, odd, out, source, records)
+    assert torch.equal(out, odd[torch.tensor([3, 49, 12, 9, 7], device="cuda")])
 
 
 def test_sampling_follows_the_distribution():
@@ -317,8 +370,9 @@ def test_sampling_follows_the_distribution():
     n = 4000
     logits = probs.log().repeat(n, 1).cuda()
     tokens = torch.empty(n, dtype=torch.int32, device="cuda")
-    zeros = torch.zeros(n, dtype=torch.int32, device="cuda")
-    o.sample(logits, torch.ones(n, device="cuda"), zeros + 77, zeros, torch.arange(n, dtype=torch.int32, device="cuda"), tokens)
+    records = make_records(o, [1.0], [77], [0]).repeat(n, 1)
+    records[:, o.RECORD_COUNT] = torch.arange(n, dtype=torch.int32, device="cuda")
+    o.sample(logits, tokens, records.contiguous(), torch.arange(n, dtype=torch.int32, device="cuda"))
     freq = torch.bincount(tokens.long().cpu(), minlength=4).float() / n
     assert (freq - probs).abs().max() < 0.03
 
@@ -621,3 +675,94 @@ def test_attention_tcgen05_scores_far_apart_force_rescaling(heads):
     assert o.attention_tcgen05_status() == 0
     expected = plain_attention(q, ks[0], vs[0])
     close(out.cpu().view(n, heads, dim), expected, torch.bfloat16)
+
+
+@pytest.mark.parametrize("kernel", ["simt", "prefill", "decode", "tcgen05"])
+def test_pools_of_more_than_2_to_the_31_elements(kernel):
+    """Pages whose element offset does not fit 32 bits (the reference pins the same for its decode
+    kernel, tests/test_triton_decode.py:277-300 there): the page-write kernel puts keys and values
+    there and each attention kernel reads them back."""
+    o = ops()
+    q_heads, kv_heads, dim, page = 32, 8, 128, 16
+    dtype = torch.float32 if kernel == "simt" else torch.bfloat16
+    pages = (1 << 31) // (kv_heads * page * dim) + 40
+    pool = torch.empty((1, 2, pages + 1, kv_heads, page, dim), dtype=dtype, device="cuda")
+    k_pool, v_pool = pool[0, 0], pool[0, 1]
+    assert k_pool.numel() > 2 ** 31
+    lengths, q_lens = [70, 33, 130], ([70, 5, 128] if kernel != "decode" else [1, 1, 1])
+    gen = torch.Generator().manual_seed(5)
+    mine, at = [], pages                                  # the sequences' pages are the pool's last ones
+    for n in lengths:
+        count = -(-n // page)
+        at -= count
+        mine.append(list(range(at, at + count)))
+    assert at * kv_heads * page * dim > 2 ** 31
+    width = max(len(m) for m in mine)
+    table = torch.full((len(lengths), width), pages, dtype=torch.int32)
+    ks, vs, slots = [], [], []
+    for s, n in enumerate(lengths):
+        table[s, :len(mine[s])] = torch.tensor(mine[s], dtype=torch.int32)
+        ks.append(torch.randn(n, kv_heads, dim, generator=gen).to(dtype))
+        vs.append(torch.randn(n, kv_heads, dim, generator=gen).to(dtype))
+        slots += [mine[s][pos // page] * page + pos % page for pos in range(n)]
+    # the write: rows of [q | k | v] without norm or rotation
+    total = sum(lengths)
+    rows = torch.cat([torch.zeros(total, q_heads * dim, dtype=dtype), torch.cat(ks).reshape(total, -1),
+                      torch.cat(vs).reshape(total, -1)], dim=1).cuda()
+    pool[:, :, at:].fill_(float("nan"))
+    o.qk_norm_rope_kv(rows, None, k_pool, v_pool, None, None, None, torch.tensor(slots, dtype=torch.int32, device="cuda"),
+                      q_heads, kv_heads, dim, page, 0.0)
+    last = mine[2][-1]
+    assert torch.equal(k_pool[last, :, (130 - 1) % page].cpu(), ks[2][-1]) and torch.equal(v_pool[mine[0][0], :, 0].cpu(), vs[0][0])
+    qs = [torch.randn(n, q_heads, dim, generator=gen).to(dtype) for n in q_lens]
+    q = torch.cat(qs).reshape(-1, q_heads * dim).cuda()
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    bq = {"simt": o.attention_simt_block_queries, "prefill": o.attention_mma_block_queries,
+          "decode": o.attention_mma_block_queries, "tcgen05": lambda: o.TCGEN05_TILE}[kernel]()
+    tiles = [(s, q0) for s, n in enumerate(q_lens) for q0 in range(0, n, bq)]
+    tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+    tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    scale, table = 1.0 / math.sqrt(dim), table.cuda()
+    if kernel == "simt":
+        o.attention_simt(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads, dim, page, scale)
+    elif kernel == "prefill":
+        o.attention_prefill_bf16(q, k_pool, v_pool, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads, dim,
+                                 page, scale)
+    elif kernel == "decode":
+        o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, ctx, None, len(lengths), q_heads, kv_heads, dim, page, scale,
+                                0, 2)
+    else:
+        o.attention_tcgen05_prefill(q, pool, 0, out, table, cu, ctx, tile_seq, tile_q0, len(tiles), q_heads, kv_heads, dim,
+                                    page, scale)
+        assert o.attention_tcgen05_status() == 0
+    expected = []
+    for s, n in enumerate(lengths):
+        full_q = torch.zeros(n, q_heads, dim, dtype=dtype)
+        full_q[n - q_lens[s]:] = qs[s]
+        expected.append(plain_attention(full_q, ks[s], vs[s], None)[n - q_lens[s]:])
+    got = out.cpu().view(-1, q_heads, dim)
+    assert not torch.isnan(got).any()
+    close(got, torch.cat(expected), dtype)
+    del pool, k_pool, v_pool
+    torch.cuda.empty_cache()
+
+
+def test_decode_attention_gives_zeros_for_a_sequence_without_keys():
+    """A length of 0 is not something the engine produces, but the exported C entry points take raw
+    arrays from any caller: such a row gets zeros, not NaN, beside normal rows."""
+    o = ops()
+    q_heads, kv_heads, dim, page = 8, 2, 128, 16
+    k_pool, v_pool, table, ks, vs = paged_setup(torch.bfloat16, [40, 1, 200], kv_heads, dim, page)
+    ctx = torch.tensor([40, 0, 200], dtype=torch.int32, device="cuda")
+    q = torch.randn(3, q_heads * dim).to(torch.bfloat16).cuda()
+    cu = torch.arange(4, dtype=torch.int32, device="cuda")
+    for splits in (1, 2, 3):
+        out = torch.full_like(q, float("nan"))
+        o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, ctx, None, 3, q_heads, kv_heads, dim, page,
+                                1.0 / math.sqrt(dim), 0, splits)
+        assert torch.equal(out[1], torch.zeros_like(out[1])) and not torch.isnan(out).any()
+        full_q = torch.zeros(40, q_heads, dim, dtype=torch.bfloat16)
+        full_q[-1] = q[0].cpu().view(q_heads, dim)
+        close(out[0].cpu().view(q_heads, dim), plain_attention(full_q, ks[0], vs[0], None)[-1], torch.bfloat16)

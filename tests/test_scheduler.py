@@ -12,41 +12,40 @@ from layover_b200.engine import Engine, EngineConfig, Request, RequestTooLarge, 
 from layover_b200.parts.base import PagedKVNeed
 
 
+class FakeTokens:
+    def __init__(self, values):
+        self.values = values
+
+    def result(self):
+        return list(self.values)
+
+
 class FakeStep:
-    """Counts tokens into the cache like the real step function and returns the entries back."""
+    """Counts tokens into the cache like the real step function; the 'token' it samples for a
+    request is the request's length so far, which makes the emitted tokens easy to predict."""
 
     max_position = 4096
 
     def __init__(self, cache):
         self.cache = cache
         self.batches = []
+        self.read_back = 0
 
-    def __call__(self, entries):
+    def sample(self, entries):
         for e in entries:
             self.cache.grow(e.seq, e.seq.num_tokens + len(e.tokens))    # must never raise under the scheduler
         self.batches.append([(e.seq.request_id, len(e.tokens), list(e.want)) for e in entries])
-        rows = []
+        tokens = []
         for e in entries:
             self.cache.commit(e.seq, e.seq.num_tokens + len(e.tokens))
-            rows += [e.seq.num_tokens] * len(e.want)
-        return torch.tensor(rows, dtype=torch.float32)[:, None]
-
-
-class FakeSampler:
-    """The 'token' is the request's length so far, which makes the emitted tokens easy to predict."""
-
-    def __init__(self):
-        self.calls = []
-
-    def __call__(self, logits, params, steps):
-        self.calls.append((list(params), list(steps)))
-        return [int(v) for v in logits[:, 0]]
+            tokens += [e.seq.num_tokens] * len(e.want)
+        return FakeTokens(tokens)
 
 
 def make(blocks=64, page=4, config=EngineConfig(), window=None, max_requests=8):
     cache = CacheManager([(0, PagedKVNeed(1, 16, window), None)], blocks, page, torch.float32, None, max_requests)
     clock = iter(range(10**6))
-    engine = Engine(None, cache, config, clock=lambda: next(clock), step_fn=FakeStep(cache), sampler=FakeSampler())
+    engine = Engine(None, cache, config, clock=lambda: next(clock), step_fn=FakeStep(cache))
     return engine, cache
 
 
@@ -154,15 +153,95 @@ def test_last_token_is_never_fed_and_timestamps_are_ordered():
     assert request.submitted_at <= request.admitted_at <= request.first_token_at <= request.finished_at
 
 
-def test_sampler_gets_each_requests_own_parameters_and_step_counts():
-    engine, _ = make()
-    engine.add_request(Request("a", [1, 1], 3, temperature=0.5, seed=7))
+def test_each_requests_sampling_parameters_go_into_its_record_at_admission():
+    import struct
+
+    from layover_b200 import ops
+
+    engine, cache = make()
+    opened = []
+    real_open = cache.open
+    cache.open = lambda rid, record=None: (opened.append((rid, record)), real_open(rid, record))[1]
+    engine.add_request(Request("a", [1, 1], 3, temperature=0.5, seed=(7 << 32) | 0xFFFFFFFE))
     engine.add_request(Request("b", [1], 2))
     engine.run_until_idle()
-    params, steps = engine.sampler.calls[0]
-    assert (params[0].temperature, params[0].seed) == (0.5, 7) and params[1].temperature == 0.0
-    assert steps == [0, 0]
-    assert engine.sampler.calls[1][1] == [1, 1]
+    (name_a, rec_a), (name_b, rec_b) = opened
+    assert (name_a, name_b) == ("a", "b") and len(rec_a) == ops.RECORD_WORDS
+    assert struct.unpack("<f", struct.pack("<i", rec_a[ops.RECORD_TEMPERATURE]))[0] == 0.5
+    assert rec_a[ops.RECORD_SEED_LO] == -2 and rec_a[ops.RECORD_SEED_HI] == 7       # the 64-bit seed as two words
+    assert rec_a[ops.RECORD_COUNT] == 0 and rec_a[ops.RECORD_POSITION] == 2
+    assert rec_b[ops.RECORD_TEMPERATURE] == 0 and rec_b[ops.RECORD_SEED_LO] == 0
+    with pytest.raises(ValueError, match="temperature"):
+        engine.add_request(Request("c", [1], 2, temperature=-1.0))
+
+
+def test_decoded_tokens_are_named_not_sent():
+    """A decoding request's newest token stays on the device: the step names it, no id travels."""
+    from layover_b200.engine.batch import DEVICE_TOKEN
+
+    engine, cache = make()
+    seen = []
+    real = engine.step_fn.sample
+    engine.step_fn.sample = lambda entries: (seen.append([list(e.tokens) for e in entries]), real(entries))[1]
+    engine.add_request(Request("a", [5, 6, 7], 3))
+    engine.run_until_idle()
+    assert seen == [[[5, 6, 7]], [[DEVICE_TOKEN]], [[DEVICE_TOKEN]]]
+
+
+def test_one_budget_for_the_whole_step_counts_decoded_tokens_first():
+    config = EngineConfig(max_batch=4, prefill_chunk=8, max_batched_tokens=10)
+    engine, _ = make(config=config)
+    engine.add_request(Request("d1", [1] * 2, 9))
+    engine.add_request(Request("d2", [1] * 2, 9))
+    engine.step()                                                   # both prompts whole: 4 tokens of 10
+    engine.add_request(Request("long", [2] * 30, 2))
+    engine.add_request(Request("long2", [2] * 30, 2))
+    engine.step()
+    # two decoded tokens first, then 8 prompt tokens (the chunk would allow 8, the rest is 8), none left for long2
+    assert engine.step_fn.batches[1] == [("d1", 1, [0]), ("d2", 1, [0]), ("long", 8, [])]
+    engine.step()
+    assert sum(n for _, n, _ in engine.step_fn.batches[2]) == 10
+    with pytest.raises(ValueError, match="max_batched_tokens"):
+        EngineConfig(max_batch=8, max_batched_tokens=4)
+    # without it the reference's rule: prefill_budget prompt tokens, decoded tokens not counted
+    engine, _ = make(config=EngineConfig(max_batch=4, prefill_chunk=8, prefill_budget=8))
+    engine.add_request(Request("d1", [1] * 2, 9))
+    engine.step()
+    engine.add_request(Request("long", [2] * 30, 2))
+    engine.step()
+    assert engine.step_fn.batches[1] == [("d1", 1, [0]), ("long", 8, [])]
+
+
+def test_ignore_eos_generates_to_the_limit():
+    engine, _ = make()
+    engine.add_request(Request("s", [9] * 5, 6, stop_tokens=frozenset({7}), ignore_eos=True))
+    engine.add_request(Request("t", [9] * 5, 6, stop_tokens=frozenset({7})))
+    engine.run_until_idle()
+    by_name = {r.request_id: r.generated for r in engine.finished}
+    assert by_name["s"] == [5, 6, 7, 8, 9, 10] and by_name["t"] == [5, 6, 7]
+
+
+def test_admission_counts_a_free_state_slot():
+    """More batch places than state slots: the third request waits for a slot, nothing raises."""
+    engine, cache = make(config=EngineConfig(max_batch=4, prefill_chunk=64, prefill_budget=64), max_requests=2)
+    for i in range(3):
+        engine.add_request(Request(str(i), [1, 2], 3))
+    engine.step()
+    assert len(engine.running) == 2 and len(engine.waiting) == 1 and cache.num_free_slots == 0
+    engine.run_until_idle()
+    assert len(engine.finished) == 3 and cache.num_free_slots == 2
+    cache.check()
+
+
+def test_a_stop_token_found_a_step_late_drops_the_token_in_flight():
+    engine, cache = make()
+    engine.add_request(Request("s", [9] * 5, 50, stop_tokens=frozenset({7})))
+    engine.add_request(Request("u", [9] * 2, 8))
+    engine.run_until_idle()                                         # pipelined
+    by_name = {r.request_id: r.generated for r in engine.finished}
+    assert by_name["s"] == [5, 6, 7] and by_name["u"] == list(range(2, 10))
+    assert engine.stats["dropped_tokens"] == 1 and cache.num_free == 64
+    cache.check()
 
 
 def test_a_window_lets_long_requests_fit_a_small_pool():
