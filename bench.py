@@ -1,26 +1,45 @@
-"""Decode and prefill throughput of the engine on one B200, Qwen3-4B shape, random weights.
+"""Decode and prefill throughput of the engine on one B200, random weights of a named Qwen3 shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config 4b|4b-fp32|8b-mixed|32b-long]
 
-A step is one decode step. The default run is the 4B shape in bfloat16 at batch 8 over the
-2,048 -> 4,096-token decode phase: the K timed steps are centred on a context of 3,072 tokens,
-the mean of that phase. One JSON line on standard output:
+A step is one decode step. Every run prints ONE JSON line on standard output.
 
-  value      decoded tokens a second, K steps timed on the device with CUDA events
+--config 4b (the default, the headline): the 4B shape in bfloat16 at batch 8 over the
+2,048 -> 4,096-token decode phase; the K timed steps are centred on a context of 3,072 tokens,
+the mean of that phase.
+
+  value      decoded tokens a second, K steps timed on the device with CUDA events; a step is what
+             serving runs: the captured decode graph with the sampling kernel in it
   e2e        the same through `layover_b200.Engine` (scheduler and sampler): host token ids in,
              host token ids out, every step
   prefill    one portion of 2,048 tokens from an empty cache; frac = flops / time / the bf16 peak
   roofline   bytes a decode step must read (every weight once + the live requests' K and V)
              / its time, against the measured copy bandwidth
   points     decode tokens a second at batch 1 and 64
+  contexts   milliseconds per step at batch 8 with the timed steps centred on 2,048 and 3,072 tokens of
+             context and, for 4,096, ending there (the context is full then)
+  kernels    the dominant kernels alone (the four products of a layer at 8 and at 2,048 tokens, the
+             decode attention at batch 1, 8 and 64, the prompt attention): microseconds and the
+             fraction of the measured peak (copy bandwidth for the decode kernels, the bf16 burst
+             rate for the prompt kernels)
+
+Before anything is timed, one decode step is run twice from the same state, replayed from its
+captured graph and launch by launch, and the logits and tokens must agree bit for bit.
+
+--config 4b-fp32: the same shape through the true 32-bit path (FFMA products): decode at batch 1
+and 8 and the prefill. --config 8b-mixed: the 8B shape, 32 requests with prompts of 128..8,192
+tokens (seeded), prompt portions of 2,048 tokens beside decoding requests, 512 new tokens each,
+through `Engine`. --config 32b-long: the 32B shape, 8 prompts of 32,768 tokens, then 256 greedy
+decode steps.
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists (else 6.65 TB/s and
 1.59 PFLOP/s, an earlier measurement of the same kind of GPU). Inputs are synthetic token ids;
-weights are seeded random values of the named shape. Weights (8 GB) are larger than the L2, so
-nothing is flushed between steps.
+weights are seeded random values of the named shape. Weights (8 GB and more) are larger than the
+L2, so nothing is flushed between steps.
 
 `--impl reference` runs the unmodified CarlGergi/Layover installed under baseline/_ref through
-its own Engine for the same metric, or prints why it cannot.
+its own Engine for the headline metric, or prints why it cannot.
 """
 
 from __future__ import annotations
@@ -40,6 +59,10 @@ sys.path.insert(0, str(ROOT))
 
 PROMPT, CONTEXT, PREFILL_TOKENS, PAGE = 2048, 4096, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+FP32_TFLOPS = 75.0       # nominal FFMA rate of the part; only the 32-bit path's prefill fraction uses it
+CONFIGS = {"4b": ("qwen3-4b", "bf16"), "4b-fp32": ("qwen3-4b", "fp32"), "8b-mixed": ("qwen3-8b", "bf16"),
+           "32b-long": ("qwen3-32b", "bf16")}
+METRIC = "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)"
 
 
 def peaks() -> tuple[dict, str]:
@@ -95,6 +118,17 @@ class ClockSampler:
                 "sm_max_mhz": max(maxima) if maxima else None, "reasons": reasons, "samples": len(clocks)}
 
 
+def config_record(cfg, model_name: str, layers_run: int, batch: int, prompt: int, seq_len: int, mean_ctx: float,
+                  graphs: bool, pk_source: str) -> dict:
+    """The `config` of a line: every size of the layers, flat. Both arms print the same keys."""
+    return {"model": model_name, "layers": cfg.num_hidden_layers, "layers_run": layers_run, "hidden": cfg.hidden_size,
+            "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
+            "global_batch": batch, "prompt_len": prompt, "seq_len": seq_len, "timed_mean_context": round(mean_ctx),
+            "block_tokens": PAGE, "parallelism": "single GPU", "cuda_graphs": graphs,
+            "l2": "inputs larger than L2 (weights of 8 GB or more), no flush", "peaks": pk_source}
+
+
 # --------------------------------------------------------------------------------------- ours
 def fill_requests(step_fn, cache, batch: int, tokens_each: int, vocab: int, gen):
     """Open `batch` requests and run `tokens_each` prompt tokens of each through the engine."""
@@ -112,41 +146,102 @@ def fill_requests(step_fn, cache, batch: int, tokens_each: int, vocab: int, gen)
     return seqs
 
 
-def decode_point(model, batch: int, steps: int, warmup: int, gen, clocks=None) -> dict:
-    """K decode steps of `batch` requests, timed on the device, centred on the middle of the decode phase."""
+def kv_bytes_per_token(model) -> int:
+    from layover_b200.parts.base import PagedKVNeed
+
+    element = 2 if str(model.dtype).endswith("bfloat16") else 4
+    return sum(need.elements_per_token() * element for _, need, reads in model.cache_needs()
+               if reads is None and isinstance(need, PagedKVNeed))
+
+
+def check_graph_replay(model, gen) -> None:
+    """One decode step, replayed from its captured graph and run launch by launch from the same
+    state (two caches filled alike): logits and sampled tokens must agree bit for bit."""
+    import torch
+    import layover_b200 as lb
+    from layover_b200.engine.step import StepFunction
+
+    vocab, batch, outputs = model.spec.vocab_size, 5, []         # 5 rows in a bucket of 8: padded rows run too
+    prompts = [torch.randint(0, vocab, (40 + 300 * i,), generator=gen).tolist() for i in range(batch)]
+    for replay in (True, False):
+        cache = lb.PagedKVCache(model, batch * 100, block_tokens=PAGE, max_requests=8)
+        step_fn = StepFunction(model, cache, cuda_graphs=True, graph_max_tokens=CONTEXT)
+        step_fn.replay_graphs = replay
+        seqs = [cache.open(f"check{i}") for i in range(batch)]
+        for seq, prompt in zip(seqs, prompts):
+            step_fn([lb.StepEntry(seq, prompt, [])])
+        logits = step_fn([lb.StepEntry(seq, [17 + i], [0]) for i, seq in enumerate(seqs)]).clone()
+        tokens = step_fn.sample([lb.StepEntry(seq, [lb.DEVICE_TOKEN], [0]) for seq in seqs]).result()
+        outputs.append((logits.cpu(), tokens))
+        if replay and step_fn.graph_replays != 2:
+            raise RuntimeError("bench.py: the decode steps of the check did not replay a graph")
+        for seq in seqs:
+            cache.close(seq)
+        del cache, step_fn
+    (graph_logits, graph_tokens), (eager_logits, eager_tokens) = outputs
+    if not torch.equal(graph_logits, eager_logits) or graph_tokens != eager_tokens:
+        worst = (graph_logits - eager_logits).abs().max().item()
+        raise RuntimeError(f"bench.py: a replayed decode step differs from the same step without a graph "
+                           f"(largest |difference| of logits {worst:.3e}): nothing was timed")
+    if not torch.isfinite(graph_logits).all():
+        raise RuntimeError("bench.py: the checked decode step has logits that are not finite")
+    torch.cuda.empty_cache()
+
+
+def decode_point(model, batch: int, steps: int, warmup: int, gen, clocks=None, centre: int | None = None,
+                 first_ctx: int | None = None, graph_tokens: int = CONTEXT) -> dict:
+    """K decode steps of `batch` requests, timed on the device, centred on the context `centre` (or
+    starting at `first_ctx`). A step is `StepFunction.sample` on the tokens the step before sampled:
+    the captured graph (with the sampling kernel), one copy in and one copy out."""
     import torch
     import layover_b200 as lb
     from layover_b200 import ops
     from layover_b200.engine.step import StepFunction
 
     vocab = model.spec.vocab_size
-    start = max(1, (PROMPT + CONTEXT) // 2 - steps // 2 - warmup)
-    pages = batch * (-(-(start + warmup + steps + 1) // PAGE))
+    if first_ctx is None:
+        centre = (PROMPT + CONTEXT) // 2 if centre is None else centre
+        first_ctx = max(1, centre - steps // 2 - warmup)
+    pages = batch * (-(-(first_ctx + warmup + steps + 1) // PAGE))
     cache = lb.PagedKVCache(model, pages, block_tokens=PAGE, max_requests=batch)
-    step_fn = StepFunction(model, cache, cuda_graphs=True, graph_sizes=(batch,), graph_max_tokens=CONTEXT)
-    seqs = fill_requests(step_fn, cache, batch, start, vocab, gen)
-    tokens = torch.randint(0, vocab, (warmup + steps, batch), generator=gen).tolist()
-    for i in range(warmup):
-        step_fn([lb.StepEntry(s, [tokens[i][j]], [0]) for j, s in enumerate(seqs)])
+    step_fn = StepFunction(model, cache, cuda_graphs=True, graph_sizes=(batch,), graph_max_tokens=graph_tokens)
+    seqs = fill_requests(step_fn, cache, batch, first_ctx - 1, vocab, gen)
+    # every graph the timed steps replay is captured now, not inside the timed region
+    step_fn.capture_all(tokens=first_ctx + warmup + steps + 1, from_tokens=first_ctx)
+    first = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+    pending = step_fn.sample([lb.StepEntry(s, [first[j]], [0]) for j, s in enumerate(seqs)])   # now every record has a token
+    entries = lambda: [lb.StepEntry(s, [lb.DEVICE_TOKEN], [0]) for s in seqs]
+    for _ in range(warmup):
+        pending.result()
+        pending = step_fn.sample(entries())
+    pending.result()
     torch.cuda.synchronize()
     launches_before = step_fn.replayed_launches + ops.LAUNCHES
-    first_ctx = seqs[0].num_tokens
+    replays_before = step_fn.graph_replays
+    start_ctx = seqs[0].num_tokens
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if clocks is not None:
         clocks.__enter__()
     begin.record()
-    for i in range(warmup, warmup + steps):
-        step_fn([lb.StepEntry(s, [tokens[i][j]], [0]) for j, s in enumerate(seqs)])
+    waiting = None
+    for _ in range(steps):
+        pending = step_fn.sample(entries())
+        if waiting is not None:
+            waiting.result()         # the host reads a step's tokens while the device runs the next
+        waiting = pending
     end.record()
     torch.cuda.synchronize()
     if clocks is not None:
         clocks.__exit__()
+    waiting.result()
     ms = begin.elapsed_time(end) / steps
-    mean_ctx = first_ctx + (steps + 1) / 2
-    kv_bytes = batch * mean_ctx * sum(2 * n.kv_heads * n.head_dim for _, n, r in model.cache_needs() if r is None) * 2
+    mean_ctx = start_ctx + (steps + 1) / 2
+    kv_bytes = batch * mean_ctx * kv_bytes_per_token(model)
     result = {"tok_s": batch * 1000.0 / ms, "ms_per_step": ms, "bytes": model.weight_bytes() + kv_bytes,
               "launches": step_fn.replayed_launches + ops.LAUNCHES - launches_before, "mean_ctx": mean_ctx,
-              "graph_replays": step_fn.graph_replays}
+              "graph_replays": step_fn.graph_replays - replays_before}
+    if result["graph_replays"] != steps:
+        raise RuntimeError("bench.py: a timed decode step did not replay its graph")
     for seq in seqs:
         cache.close(seq)
     del cache, step_fn
@@ -219,9 +314,10 @@ def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
     if len(engine.running) != batch:
         raise RuntimeError("a request finished inside the timed steps: the end-to-end number would be wrong")
     produced = sum(len(r.generated) for r in engine.running) - produced
-    width = engine.step_fn.graph_table_width
+    width = engine.step_fn.graph_width_for(cache.blocks_for(start + budget))
     h2d = 4 * lb.engine.BatchBuilder.buffer_size(lb.engine.BatchCapacity(batch, width), len(cache.paged), model.tile_sizes())
-    return {"value": produced / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+    d2h = 4 * (batch + engine.step_fn.sampler.n_status)
+    return {"value": produced / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "ms_per_step": 1000.0 * elapsed / steps}
 
 
@@ -252,20 +348,22 @@ def graph_time(fn, calls: int, reps: int = 10) -> float:
     return begin.elapsed_time(end) / reps / calls
 
 
-def kernel_points(args) -> dict:
+def kernel_points(model_name: str, pk: dict, with_library: bool) -> dict:
     """The dominant kernels alone at the benchmark's shapes, each over rotating operands larger than
     the L2: the four products of a layer at 8 and 2,048 tokens (with torch.mm, i.e. cuBLAS, beside
-    them for scale) and the decode attention at batch 1, 8 and 64."""
+    them for scale when `with_library`), the decode attention at batch 1, 8 and 64 and the prompt
+    attention. `frac` is of the measured peak: copy bandwidth for the few-token products and the
+    decode attention, the bf16 burst rate for the 2,048-token products and the prompt attention."""
     import math
     import torch
     import layover_b200 as lb
     from layover_b200 import ops
 
-    cfg = lb.preset(args.model)
+    cfg = lb.preset(model_name)
     d, nq, nkv, h, inter = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size, cfg.intermediate_size
     shapes = {"qkv": ((nq + 2 * nkv) * d, h), "o": (h, nq * d), "gate_up": (2 * inter, h), "down": (h, inter)}
     ops.gemm_scratch("cuda"); ops.attention_scratch("cuda")
-    out = {"gemm": {}, "attention_decode": {}}
+    out = {}
     for tokens in (8, PREFILL_TOKENS):
         for name, (n, k) in shapes.items():
             copies = 24 if tokens <= 128 else 4
@@ -273,10 +371,15 @@ def kernel_points(args) -> dict:
             a = torch.randn(tokens, k, device="cuda").to(torch.bfloat16)
             c = torch.empty(tokens, n, device="cuda", dtype=torch.bfloat16)
             ours = graph_time(lambda i: ops.gemm_tcgen05(a, weights[i % copies], c), copies)
-            lib = graph_time(lambda i: torch.mm(a, weights[i % copies].T, out=c), copies)
-            out["gemm"][f"{name}_m{tokens}"] = {
-                "us": round(ours * 1e3, 1), "cublas_us": round(lib * 1e3, 1),
-                "tb_s": round(n * k * 2 / ours / 1e9, 2), "tflops": round(2.0 * tokens * n * k / ours / 1e9, 0)}
+            row = {"us": round(ours * 1e3, 1)}
+            if tokens <= 128:
+                row["frac"] = round(n * k * 2 / (ours * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
+            else:
+                row["frac"] = round(2.0 * tokens * n * k / (ours * 1e-3) / 1e12 / pk["bf16_tflops"], 3)
+            if with_library:
+                lib = graph_time(lambda i: torch.mm(a, weights[i % copies].T, out=c), copies)
+                row["cublas_us"] = round(lib * 1e3, 1)
+            out[f"{name}_m{tokens}"] = row
             del weights
     page, ctx = PAGE, (PROMPT + CONTEXT) // 2
     for batch in (1, 8, 64):
@@ -291,8 +394,8 @@ def kernel_points(args) -> dict:
         splits = ops.decode_splits(batch, nq, nkv, d, ctx, torch.cuda.get_device_properties(0).multi_processor_count)
         t = graph_time(lambda i: ops.attention_decode_bf16(q, pools[i % layers, 0], pools[i % layers, 1], o, table, cu, lens,
                                                            None, batch, nq, nkv, d, page, 1 / math.sqrt(d), 0, splits), layers)
-        out["attention_decode"][f"b{batch}_ctx{ctx}"] = {
-            "us": round(t * 1e3, 1), "splits": splits, "tb_s": round(batch * ctx * nkv * d * 4 / t / 1e9, 2)}
+        out[f"attn_decode_b{batch}"] = {"us": round(t * 1e3, 1), "splits": splits,
+                                        "frac": round(batch * ctx * nkv * d * 4 / (t * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
         del pools
     # one prompt of 2,048 tokens through the prompt-portion attention (tcgen05 where it takes the sizes)
     tokens = PREFILL_TOKENS
@@ -311,9 +414,162 @@ def kernel_points(args) -> dict:
         t = graph_time(lambda i: ops.attention_tcgen05_prefill(q, pools, i % layers, o, table, cu, lens, tile_seq, tile_q0,
                                                                n_tiles, nq, nkv, d, page, 1 / math.sqrt(d), 0), layers)
         flops = 4.0 * nq * d * tokens * (tokens + ops.TCGEN05_TILE) / 2      # both products, causal tiles
-        out["attention_prefill"] = {f"t{tokens}": {"us": round(t * 1e3, 1), "tflops": round(flops / t / 1e9, 0)}}
+        out[f"attn_prefill_t{tokens}"] = {"us": round(t * 1e3, 1),
+                                          "frac": round(flops / (t * 1e-3) / 1e12 / pk["bf16_tflops"], 3)}
         del pools
-    return {"only": "kernels", **out, "gemm_status": ops.gemm_status(), "attention_status": ops.attention_tcgen05_status()}
+    if ops.gemm_status() or ops.attention_tcgen05_status():
+        raise RuntimeError("bench.py: a tensor-core kernel reported a wait that ran out")
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_4b(args, cfg, model, gen, pk, pk_source) -> dict:
+    clocks = ClockSampler()
+    check_graph_replay(model, gen)
+    main = decode_point(model, args.batch, args.steps, args.warmup, gen, clocks)
+    few = max(16, min(64, args.steps // 4))
+    # centred on 2,048 and 3,072; at 4,096 the context is full, so those are the last steps that end there
+    contexts = {str(label): round(decode_point(model, args.batch, few, args.warmup, gen, centre=centre)["ms_per_step"], 4)
+                for label, centre in ((PROMPT, PROMPT), ((PROMPT + CONTEXT) // 2, (PROMPT + CONTEXT) // 2),
+                                      (CONTEXT, CONTEXT - few // 2 - 1))}
+    prefill = prefill_point(model, gen)
+    points = {}
+    for batch in (1, 64):
+        points[f"decode_b{batch}"] = round(decode_point(model, batch, max(16, args.steps // 2), args.warmup, gen)["tok_s"], 1)
+    e2e = e2e_point(model, args.batch, max(16, args.steps // 2), args.warmup, gen)
+    kernels = kernel_points(args.model, pk, with_library=False) if args.dtype == "bf16" and not args.layers else {}
+    achieved = main["bytes"] / (main["ms_per_step"] * 1e-3) / 1e9
+    flops = prefill_flops(cfg, cfg.num_hidden_layers, PREFILL_TOKENS)
+    tflops_peak = pk["bf16_tflops"] if args.dtype == "bf16" else FP32_TFLOPS
+    return {
+        "metric": METRIC, "value": round(main["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "config": config_record(lb_preset(args.model), args.model, cfg.num_hidden_layers, args.batch, PROMPT, CONTEXT,
+                                main["mean_ctx"], True, pk_source),
+        "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": main["launches"],
+        "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
+                    "frac": round(flops / (prefill["ms"] * 1e-3) / (tflops_peak * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "contexts": contexts,
+        "kernels": kernels,
+        "graph_check": "replayed step == the same step launch by launch, bit for bit",
+        "clocks": clocks.summary(),
+    }
+
+
+def run_4b_fp32(args, cfg, model, gen, pk, pk_source) -> dict:
+    """The true 32-bit path at the headline's shape: reported, not the headline."""
+    clocks = ClockSampler()
+    steps = min(args.steps, 32)
+    main = decode_point(model, 8, steps, args.warmup, gen, clocks)
+    one = decode_point(model, 1, steps, args.warmup, gen)
+    prefill = prefill_point(model, gen, repeats=3)
+    flops = prefill_flops(cfg, cfg.num_hidden_layers, PREFILL_TOKENS)
+    achieved = main["bytes"] / (main["ms_per_step"] * 1e-3) / 1e9
+    return {
+        "metric": "decode tokens/s (Qwen3-4B shape, true 32-bit path, batch 8, context 2048->4096)",
+        "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "config": config_record(lb_preset(args.model), args.model, cfg.num_hidden_layers, 8, PROMPT, CONTEXT, main["mean_ctx"],
+                                True, pk_source),
+        "gpu_launches": main["launches"],
+        "points": {"decode_b1": round(one["tok_s"], 1), "decode_b8": round(main["tok_s"], 1)},
+        "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
+                    "frac": round(flops / (prefill["ms"] * 1e-3) / (FP32_TFLOPS * 1e12), 4), "peak_tflops": FP32_TFLOPS},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "clocks": clocks.summary(),
+    }
+
+
+def run_8b_mixed(args, cfg, model, gen, pk, pk_source) -> dict:
+    """32 requests with prompts of 128..8,192 tokens, prompt portions of 2,048 tokens beside decoding
+    requests, 512 new tokens each, through `Engine` with captured decode steps and pipelined stepping."""
+    import torch
+    import layover_b200 as lb
+
+    requests, new_tokens, chunk = 32, 512, 2048
+    lengths = torch.randint(128, 8193, (requests,), generator=gen).tolist()
+    pages = sum(-(-(n + new_tokens) // PAGE) for n in lengths)
+    cache = lb.PagedKVCache(model, pages, block_tokens=PAGE, max_requests=requests)
+    engine = lb.Engine(model, cache, lb.EngineConfig(requests, chunk, chunk), cuda_graphs=True)
+    # graphs are captured before the clock starts
+    engine.step_fn.capture_all(tokens=max(lengths) + new_tokens, from_tokens=min(lengths))
+    for i, n in enumerate(lengths):
+        engine.add_request(lb.Request(str(i), torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist(), new_tokens))
+    clocks = ClockSampler()
+    step_ms = []
+    torch.cuda.synchronize()
+    with clocks:
+        began = time.perf_counter()
+        last = began
+        while not (engine.idle and engine._inflight is None):
+            engine.step_pipelined()
+            now = time.perf_counter()
+            step_ms.append((now - last) * 1e3)
+            last = now
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - began
+    finished = engine.finished
+    if len(finished) != requests or any(len(r.generated) != new_tokens for r in finished):
+        raise RuntimeError("bench.py: not every request of the mixed run finished with all its tokens")
+    generated = sum(len(r.generated) for r in finished)
+    ttft = sorted((r.first_token_at - r.submitted_at) * 1e3 for r in finished)
+    step_ms.sort()
+    pick = lambda values, q: round(values[min(len(values) - 1, int(q * len(values)))], 2)
+    return {
+        "metric": "generated tokens/s (Qwen3-8B shape, 32 requests, prompts 128..8192, portions of 2048, 512 new tokens each)",
+        "value": round(generated / elapsed, 1), "unit": "tokens/s", "n_gpus": 1, "steps": engine.stats["steps"], "warmup": 0,
+        "ms_per_step": round(1e3 * elapsed / max(1, engine.stats["steps"]), 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "config": config_record(lb_preset(args.model), args.model, cfg.num_hidden_layers, requests, sum(lengths) // requests,
+                                max(lengths) + new_tokens, sum(lengths) / requests + new_tokens / 2, True, pk_source),
+        "seconds": round(elapsed, 3), "prompt_tokens": sum(lengths), "generated_tokens": generated,
+        "total_tokens_per_s": round((sum(lengths) + generated) / elapsed, 1),
+        "ttft_ms": {"p50": pick(ttft, 0.5), "p90": pick(ttft, 0.9), "max": round(ttft[-1], 2)},
+        "step_ms": {"p50": pick(step_ms, 0.5), "p90": pick(step_ms, 0.9), "p99": pick(step_ms, 0.99), "max": round(step_ms[-1], 2)},
+        "pool": {"pages": pages, "gib": round(cache.pool_bytes() / 2**30, 2)},
+        "engine": dict(engine.stats), "graph_replays": engine.step_fn.graph_replays,
+        "gpu_launches": engine.step_fn.replayed_launches,
+        "clocks": clocks.summary(),
+    }
+
+
+def run_32b_long(args, cfg, model, gen, pk, pk_source) -> dict:
+    """8 prompts of 32,768 tokens, then 256 greedy decode steps timed on the device."""
+    batch, prompt, steps = 8, 32768, args.steps
+    clocks = ClockSampler()
+    began = time.perf_counter()
+    point = decode_point(model, batch, steps, args.warmup, gen, clocks, first_ctx=prompt + 1, graph_tokens=prompt + steps + 64)
+    achieved = point["bytes"] / (point["ms_per_step"] * 1e-3) / 1e9
+    return {
+        "metric": "decode tokens/s (Qwen3-32B shape, 8 requests of 32,768-token prompts, 256 greedy steps)",
+        "value": round(point["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": round(point["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "config": config_record(lb_preset(args.model), args.model, cfg.num_hidden_layers, batch, prompt, prompt + steps,
+                                point["mean_ctx"], True, pk_source),
+        "gpu_launches": point["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(point["bytes"])},
+        "seconds_with_prefill": round(time.perf_counter() - began, 1),
+        "clocks": clocks.summary(),
+    }
+
+
+def lb_preset(name: str):
+    import layover_b200 as lb
+    return lb.preset(name)
+
+
+def parser_default(name: str):
+    return {"steps": 256, "warmup": 8}[name]
 
 
 def run_ours(args) -> dict:
@@ -322,15 +578,14 @@ def run_ours(args) -> dict:
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    pk, pk_source = peaks()
     if args.only == "kernels":
-        return kernel_points(args)
+        return {"only": "kernels", **kernel_points(args.model, pk, with_library=True)}
     cfg = lb.preset(args.model)
-    layers_full = cfg.num_hidden_layers
     if args.layers:
         cfg = cfg.replace(num_hidden_layers=args.layers)
     gen = torch.Generator().manual_seed(0)
     model = lb.random_model(cfg, seed=0, device="cuda", dtype=args.dtype, std=0.02)
-    pk, pk_source = peaks()
     if args.only == "decode":
         point = decode_point(model, args.batch, args.steps, args.warmup, gen)
         return {"only": "decode", "batch": args.batch, "layers_run": cfg.num_hidden_layers,
@@ -339,40 +594,14 @@ def run_ours(args) -> dict:
         point = prefill_point(model, gen, repeats=max(1, args.steps))
         return {"only": "prefill", "layers_run": cfg.num_hidden_layers, "tok_s": round(point["tok_s"], 1),
                 "ms": round(point["ms"], 3)}
-    clocks = ClockSampler()
-    main = decode_point(model, args.batch, args.steps, args.warmup, gen, clocks)
-    prefill = prefill_point(model, gen)
-    points = {}
-    for batch in (1, 64):
-        points[f"decode_b{batch}"] = round(decode_point(model, batch, max(16, args.steps // 2), args.warmup, gen)["tok_s"], 1)
-    e2e = e2e_point(model, args.batch, max(16, args.steps // 2), args.warmup, gen)
-    achieved = main["bytes"] / (main["ms_per_step"] * 1e-3) / 1e9
-    flops = prefill_flops(cfg, cfg.num_hidden_layers, PREFILL_TOKENS)
-    tflops_peak = pk["bf16_tflops"] if args.dtype == "bf16" else 75.0
-    return {
-        "metric": "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)", "value": round(main["tok_s"], 1),
-        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "impl": "ours",
-        "config": {"model": args.model, "layers": layers_full, "layers_run": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
-                   "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
-                   "global_batch": args.batch, "prompt_len": PROMPT, "seq_len": CONTEXT, "timed_mean_context": round(main["mean_ctx"]),
-                   "block_tokens": PAGE, "parallelism": "single GPU", "cuda_graphs": True,
-                   "l2": "inputs larger than L2 (weights 8 GB), no flush", "peaks": pk_source},
-        "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
-        "gpu_launches": main["launches"],
-        "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
-                    "frac": round(flops / (prefill["ms"] * 1e-3) / (tflops_peak * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points,
-        "clocks": clocks.summary(),
-    }
+    runner = {"4b": run_4b, "4b-fp32": run_4b_fp32, "8b-mixed": run_8b_mixed, "32b-long": run_32b_long}[args.config]
+    return runner(args, cfg, model, gen, pk, pk_source)
 
 
 # --------------------------------------------------------------------------------------- the reference
 def run_reference(args) -> dict:
+    if args.config != "4b":
+        return {"impl": "reference", "unavailable": f"the reference arm runs the headline (--config 4b), not {args.config}"}
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "layover").is_dir():
         return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference)"}
@@ -407,12 +636,12 @@ def run_reference(args) -> dict:
     slack = batch * (-(-start // PREFILL_TOKENS)) + 8      # tokens decoded while other prompts still prefill
     blocks = batch * (-(-(start + warmup + steps + slack + 2) // PAGE)) + 2
     cache = PagedKVCache(cfg, blocks, "cuda", torch.bfloat16, PAGE)
-    graphs = False
+    graphs, graph_width = False, 0
     if backend == "triton" and batch <= 8:
         try:
             from layover.decode_graphs import DecodeGraphs
             model.decode_graphs = DecodeGraphs(model, cache, max_tokens=CONTEXT)
-            graphs = True
+            graphs, graph_width = True, model.decode_graphs.width
         except Exception:
             model.decode_graphs = None
     engine = Engine(model, cache, EngineConfig(batch, PREFILL_TOKENS, PREFILL_TOKENS))
@@ -427,6 +656,7 @@ def run_reference(args) -> dict:
         for _ in range(warmup):
             engine.step()
         torch.cuda.synchronize()
+        first_ctx = max(r.table.num_tokens for r in engine.running)
         produced = sum(len(r.generated) for r in engine.running)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with clocks:
@@ -455,15 +685,24 @@ def run_reference(args) -> dict:
         prefill_ms = statistics.median(times[1:])
     except Exception as error:
         return {"impl": "reference", "unavailable": f"the reference failed on this GPU: {type(error).__name__}: {error}"[:240]}
+    # what its decode step copies to the device: the packed rows [rows, 3 + table width] of int32
+    # (layover/kv/paged_cache.py:154-169, layover/decode_graphs.py:87-91) and the tokens as int64
+    if graphs:
+        rows = next(s for s in model.decode_graphs.sizes if s >= batch)
+        h2d = 4 * rows * (3 + graph_width) + 8 * batch
+    else:
+        h2d = 4 * batch * (3 + cache.blocks_for(first_ctx + steps)) + 8 * batch
+    _, pk_source = peaks()
     return {
-        "metric": "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)", "value": round(batch * 1000.0 / device_ms, 1),
+        "metric": METRIC, "value": round(batch * 1000.0 / device_ms, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(device_ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, torch default random weights", "impl": "reference",
-        "config": {"model": args.model, "layers": cfg.num_hidden_layers, "layers_run": cfg.num_hidden_layers,
-                   "global_batch": batch, "prompt_len": PROMPT, "seq_len": CONTEXT, "block_tokens": PAGE,
-                   "decode_backend": backend, "cuda_graphs": graphs, "parallelism": "single GPU"},
-        "e2e": {"value": round(produced / elapsed, 2), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": 8 * batch},
+        "config": config_record(ours, args.model, cfg.num_hidden_layers, batch, PROMPT, CONTEXT,
+                                first_ctx + (steps + 1) / 2, graphs, pk_source),
+        "decode_backend": backend,
+        "e2e": {"value": round(produced / elapsed, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 8 * batch},
         "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3)},
         "clocks": clocks.summary(),
     }
@@ -472,20 +711,26 @@ def run_reference(args) -> dict:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=256)
-    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--steps", type=int, default=parser_default("steps"))
+    parser.add_argument("--warmup", type=int, default=parser_default("warmup"))
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--model", default="qwen3-4b")
-    parser.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    parser.add_argument("--config", default="4b", choices=sorted(CONFIGS),
+                        help="4b: the headline; 4b-fp32: the 32-bit path; 8b-mixed: 32 mixed requests through the "
+                             "scheduler; 32b-long: 8 x 32,768-token contexts")
+    parser.add_argument("--model", default=None, help="a preset's name instead of the one --config names")
+    parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the shape has (both numbers are reported)")
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                         help="decode or prefill alone, as a small target for a profiler, or the dominant kernels "
-                             "alone (prints a short line)")
+                             "alone with cuBLAS beside them (prints a short line)")
     args = parser.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    model, dtype = CONFIGS[args.config]
+    args.model = args.model or model
+    args.dtype = args.dtype or dtype
     args.warmup = max(3, args.warmup)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

@@ -206,12 +206,16 @@ class StepFunction:
         self._graphs[(size, width, sampled)] = graph
         return graph
 
-    def capture_all(self, tokens: int | None = None, sampled: bool = True) -> None:
-        """Capture every batch-size bucket now for requests of up to `tokens` tokens (default: the
-        widest table), largest first so that the smaller ones fit in its memory pool."""
-        width = self.graph_width_for(self.cache.blocks_for(tokens)) if tokens else self.graph_table_width
-        if width is None:
+    def capture_all(self, tokens: int | None = None, sampled: bool = True, from_tokens: int | None = None) -> None:
+        """Capture now, instead of at first use, every batch-size bucket for requests that hold between
+        `from_tokens` (default: `tokens`) and `tokens` tokens (default: the widest table): every
+        block-table bucket in that range, largest first so that the smaller ones fit in its memory pool."""
+        top = self.graph_width_for(self.cache.blocks_for(tokens)) if tokens else self.graph_table_width
+        if top is None:
             raise ValueError(f"{tokens} tokens are more than a captured step can hold")
-        for size in reversed(self.graph_sizes):
-            if (size, width, sampled) not in self._graphs:
-                self._capture(size, width, sampled)
+        low = self.graph_width_for(self.cache.blocks_for(from_tokens)) if from_tokens else top
+        widths = sorted({w for w in (self.graph_width_for(p) for p in range(low, top + 1)) if w is not None}, reverse=True)
+        for width in widths:
+            for size in reversed(self.graph_sizes):
+                if (size, width, sampled) not in self._graphs:
+                    self._capture(size, width, sampled)

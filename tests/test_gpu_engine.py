@@ -275,10 +275,17 @@ def test_a_layer_may_run_twice_and_a_layer_may_read_another_layers_pages(tiny_fo
 
 
 # ------------------------------------------------------------------ a toy mixer with state of its own
-def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
+@pytest.mark.parametrize("own_kernel", [False, True])
+def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path, own_kernel):
     """A mixer defined here, not in the package: a per-request running mean of the inputs, kept in
     a fixed-size state slot, projected by one matrix. Registered, built from a model folder and
-    stepped through the same step function, with no change to the package."""
+    stepped through the same step function, with no change to the package. With `own_kernel` its
+    forward launches a CUDA kernel of its own, from a source file of this test folder that it
+    registers with the package's builder and names in `kernel_libraries`: it is compiled with the
+    model's other kernels before the first step."""
+    import ctypes
+
+    from layover_b200.csrc import build
     from layover_b200.config import register_architecture, unregister_architecture
     from layover_b200.engine.step import StepFunction
     from layover_b200.models import ModelSpec, LayerSpec
@@ -301,8 +308,18 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
             super().bind(tensors, runtime)
             self.weight = tensors[self.name]
 
+        def kernel_libraries(self, dtype):
+            return ("toy_running_mean",) if own_kernel else ()
+
         def forward(self, h, batch, cache):
             out = torch.empty_like(h)
+            if own_kernel:
+                fn = build.load("toy_running_mean").toy_running_mean
+                fn.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+                code = fn(h.data_ptr(), out.data_ptr(), cache.state.data_ptr(), batch.cu_q.data_ptr(),
+                          batch.state_slots.data_ptr(), batch.n_seqs, self.hidden, torch.cuda.current_stream().cuda_stream)
+                assert code == 0
+                return self.runtime.linear(out, self.weight)
             cu, slots = batch.cu_q.tolist(), batch.state_slots.tolist()   # a toy may read back; the engine's parts do not
             for s in range(batch.n_seqs):
                 rows = h[cu[s]:cu[s + 1]].float()
@@ -340,11 +357,16 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
 
     register_mixer("running_mean", RunningMean)
     register_architecture("ToyMeanForCausalLM", "toy_mean", ToyConfig, toy_model_spec)
+    if own_kernel:
+        build.register_source("toy_running_mean", ROOT / "tests" / "toy_kernels" / "running_mean.cu")
     try:
         raw = {"architectures": ["ToyMeanForCausalLM"], "model_type": "toy_mean", "vocab_size": 50, "hidden_size": 24,
                "inter": 40, "layers": 2, "eps": 1e-5}
         lb.write_model_folder(ToyConfig(raw), tmp_path, seed=3, std=0.3, norm_std=0.1, store_dtype=torch.float32)
         model = lb.load_model(tmp_path, device="cuda", dtype="fp32")       # the class is chosen by config.json
+        if own_kernel:
+            assert "toy_running_mean" in model.kernel_libraries(torch.float32)
+            assert build.library_path("toy_running_mean").is_file()        # compiled when the model was built
         assert [n[1] for n in model.cache_needs()] == [StateNeed((25,), torch.float32)] * 2
         cache = lb.PagedKVCache(model, 4, block_tokens=4, max_requests=3)
         assert len(cache.paged) == 0 and cache.states[0].pool.shape == (2, 4, 25)
