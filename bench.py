@@ -297,6 +297,7 @@ def e2e_point(model, batch: int, steps: int, warmup: int, gen) -> dict:
     engine = lb.Engine(model, cache, lb.EngineConfig(batch, PREFILL_TOKENS, PREFILL_TOKENS), cuda_graphs=True)
     engine.step_fn.graph_sizes = (batch,)
     engine.step_fn.graph_table_width = cache.blocks_for(CONTEXT)
+    engine.step_fn.capture_all(tokens=start + budget, from_tokens=start)     # not inside the timed steps
     for i in range(batch):
         prompt = torch.randint(0, vocab, (start,), generator=gen).tolist()
         engine.add_request(lb.Request(str(i), prompt, budget))

@@ -27,6 +27,19 @@ constexpr int ROWS_PER_WARP = BQ / WARPS;
 constexpr int MAX_DIM = 256;
 constexpr int ACC_PER_LANE = MAX_DIM / 32;
 
+// four neighbouring elements with one load (the head size is a multiple of 4 and rows are 16-byte aligned)
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct Quad<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
@@ -34,7 +47,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads,
                             int kv_heads, int dim, int page_tokens, float scale, int window) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   float* q_s = smem;                               // [BQ][dim]
@@ -69,18 +82,20 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
 
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     __syncthreads();  // the previous tile is no longer read (and q_s is complete)
-    for (int i = threadIdx.x; i < BKEYS * dim; i += blockDim.x) {
-      const int j = i / dim, c = i % dim;
+    const int quads = dim >> 2;
+    for (int i = threadIdx.x; i < BKEYS * quads; i += blockDim.x) {
+      const int j = i / quads, c = (i - j * quads) << 2;
       const int key = tile * BKEYS + j;
-      float kv = 0.f, vv = 0.f;
+      float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
       if (key >= key_lo && key <= p_last) {
         const size_t page = (size_t)table[key / page_tokens];
         const size_t at = ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * dim + c;
-        kv = Elem<T>::load(k_pool + at);
-        vv = Elem<T>::load(v_pool + at);
+        kv = Quad<T>::load(k_pool + at);
+        vv = Quad<T>::load(v_pool + at);
       }
-      k_s[j * (dim + 1) + c] = kv;
-      v_s[j * dim + c] = vv;
+      float* kd = k_s + j * (dim + 1) + c;
+      kd[0] = kv.x; kd[1] = kv.y; kd[2] = kv.z; kd[3] = kv.w;
+      *reinterpret_cast<float4*>(v_s + j * dim + c) = vv;
     }
     __syncthreads();
     const int key = tile * BKEYS + lane;
@@ -135,7 +150,7 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
                                 const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
                                 int dim, int page_tokens, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (dim <= 0 || dim > MAX_DIM || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
+  if (dim <= 0 || dim > MAX_DIM || dim % 4 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
   const size_t smem = (size_t)(BQ * dim + BKEYS * (dim + 1) + BKEYS * dim) * sizeof(float);
   dim3 grid(n_tiles, q_heads);
   if (dtype == LB_F32) {

@@ -94,6 +94,79 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restr
   }
 }
 
+// The same product for steps of at most 16 tokens: tiles of 16 tokens x 16 weight rows, so that a
+// weight matrix of a few thousand rows still gives every SM a block (the 64 x 64 tiles above leave
+// most of the GPU idle then and spend 7/8 of their arithmetic on rows that are not there). A thread
+// owns one weight row and two tokens; the next slab of 32 k is fetched into registers while the
+// current one is used. Every output element is still ONE sequential fused-multiply-add chain over
+// k = 0..K-1 starting from zero, so it has the bits the large-tile kernel gives the same token.
+constexpr int FT_M = 16, FT_N = 16, FT_K = 32, FT_THREADS = 128;
+
+template <typename T>
+__device__ __forceinline__ void fetch_quad(const T* __restrict__ base, long ld, int row, int n_rows, int k, int K, bool vec,
+                                           float (&v)[4]) {
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (row >= n_rows) return;
+  const T* p = base + (long)row * ld + k;
+  if (vec && k + 3 < K) {
+    Vec4<T>::load(p, v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (k + j < K) v[j] = Elem<T>::load(p + j);
+  }
+}
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(FT_THREADS)
+gemm_simt_fewtoken_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
+                          long lda, long ldw, long ldc, bool vec_a, bool vec_w) {
+  __shared__ float As[FT_K][FT_M + 1];
+  __shared__ float Ws[FT_K][FT_N + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n0 = blockIdx.x * FT_N, m0 = blockIdx.y * FT_M;
+  const int lr = threadIdx.x >> 3, lk = (threadIdx.x & 7) * 4;      // the row and the four k this thread fetches of a slab
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;           // weight row of the tile, pair of tokens
+  float acc[2] = {0.f, 0.f};
+  float next_a[4], next_w[4];
+  fetch_quad<TA>(A, lda, m0 + lr, M, lk, K, vec_a, next_a);
+  fetch_quad<TA>(W, ldw, n0 + lr, N, lk, K, vec_w, next_w);
+  for (int k0 = 0; k0 < K; k0 += FT_K) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { As[lk + j][lr] = next_a[j]; Ws[lk + j][lr] = next_w[j]; }
+    __syncthreads();
+    if (k0 + FT_K < K) {
+      fetch_quad<TA>(A, lda, m0 + lr, M, k0 + FT_K + lk, K, vec_a, next_a);
+      fetch_quad<TA>(W, ldw, n0 + lr, N, k0 + FT_K + lk, K, vec_w, next_w);
+    }
+    const int steps = min(FT_K, K - k0);
+    if (steps == FT_K) {
+#pragma unroll
+      for (int k = 0; k < FT_K; ++k) {
+        const float w = Ws[k][tx];
+        acc[0] = fmaf(As[k][2 * ty], w, acc[0]);
+        acc[1] = fmaf(As[k][2 * ty + 1], w, acc[1]);
+      }
+    } else {
+      for (int k = 0; k < steps; ++k) {      // the k beyond K would add exact zeros; they are left out all the same
+        const float w = Ws[k][tx];
+        acc[0] = fmaf(As[k][2 * ty], w, acc[0]);
+        acc[1] = fmaf(As[k][2 * ty + 1], w, acc[1]);
+      }
+    }
+    __syncthreads();
+  }
+  const int col = n0 + tx;
+  if (col < N) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = m0 + 2 * ty + i;
+      if (row < M) Elem<TC>::store(C + (long)row * ldc + col, acc[i]);
+    }
+  }
+}
+
 template <typename T> bool vec_ok(const void* p, long ld) {
   return ((uintptr_t)p % (4 * sizeof(T)) == 0) && (ld % 4 == 0);
 }
@@ -104,6 +177,21 @@ LB_EXPORT int lb_gemm_simt(int in_dtype, int out_dtype, const void* A, const voi
                            long lda, long ldw, long ldc, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return LB_ERR_SIZE;
+  if (M <= FT_M) {
+    dim3 few((N + FT_N - 1) / FT_N, 1);
+    if (in_dtype == LB_F32 && out_dtype == LB_F32)
+      lb_launch(gemm_simt_fewtoken_kernel<float, float>, few, FT_THREADS, 0, stream, (const float*)A, (const float*)W, (float*)C,
+                M, N, K, lda, ldw, ldc, vec_ok<float>(A, lda), vec_ok<float>(W, ldw));
+    else if (in_dtype == LB_BF16 && out_dtype == LB_BF16)
+      lb_launch(gemm_simt_fewtoken_kernel<bf16, bf16>, few, FT_THREADS, 0, stream, (const bf16*)A, (const bf16*)W, (bf16*)C, M, N,
+                K, lda, ldw, ldc, vec_ok<bf16>(A, lda), vec_ok<bf16>(W, ldw));
+    else if (in_dtype == LB_BF16 && out_dtype == LB_F32)
+      lb_launch(gemm_simt_fewtoken_kernel<bf16, float>, few, FT_THREADS, 0, stream, (const bf16*)A, (const bf16*)W, (float*)C, M,
+                N, K, lda, ldw, ldc, vec_ok<bf16>(A, lda), vec_ok<bf16>(W, ldw));
+    else
+      return LB_ERR_DTYPE;
+    return lb_last_error();
+  }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return LB_ERR_SIZE;
   if (in_dtype == LB_F32 && out_dtype == LB_F32)

@@ -30,128 +30,18 @@
 #include <cudaTypedefs.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
-constexpr int BM = 128;          // rows of the MMA's M side
-constexpr int BK = 64;           // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
 constexpr int SMEM_BUDGET = 200 * 1024;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ int g_gemm_error = 0;   // 0 = ok; a wait ran out in 1 the producer, 2 the MMA issuer, 3 the epilogue, 4 the split sum
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// true when the phase with the given parity has completed; false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (spin > 1024) __nanosleep(64);
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// arrives on the barrier once every MMA issued so far by this thread has finished
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// K-major operand tile with 128-byte swizzle, as TMA wrote it: rows of 128 bytes, groups of 8 rows
-// 1024 bytes apart. Start address, leading offset (unused: 1), stride offset, version 1, layout 2.
-__device__ __forceinline__ uint64_t smem_desc(const void* tile) {
-  const uint32_t lo = ((smem_u32(tile) >> 4) & 0x3FFFu) | (1u << 16);
-  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-  return ((uint64_t)hi << 32) | lo;
-}
-// bf16 x bf16 -> f32, both K-major, M = 128, N = n
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-template <typename OutT> __device__ __forceinline__ void store_one(OutT* p, float v);
-template <> __device__ __forceinline__ void store_one<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void store_one<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
-
-template <typename OutT> __device__ __forceinline__ void store_row16(OutT* p, const float (&v)[16]);
-template <> __device__ __forceinline__ void store_row16<float>(float* p, const float (&v)[16]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-}
-template <> __device__ __forceinline__ void store_row16<bf16>(bf16* p, const float (&v)[16]) {
-  uint32_t w[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    w[i] = *reinterpret_cast<const uint32_t*>(&pair);
-  }
-  reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-  reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-}
 
 // Persistent blocks, each over its share of the work. Shared memory holds a ring of stages
 // (one 128 x 64 tile of the 128-row operand and one BN x 64 tile of the other); tensor memory holds
 // two accumulators, so the epilogue of one tile overlaps the MMAs of the next.
 constexpr int SMALL_THREADS = 128;
-
-// silu(g) * u as the reference's bfloat16 tensors compute it: the two projections round to bf16,
-// the activation rounds to bf16, the product rounds when it is stored (layover/model.py:152-153).
-__device__ __forceinline__ float swiglu_bf16(float g, float u) {
-  g = __bfloat162float(__float2bfloat16_rn(g));
-  u = __bfloat162float(__float2bfloat16_rn(u));
-  const float act = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
-  return act * u;
-}
 
 // With the SwiGLU epilogue the weight's rows come in blocks of 128: 64 gate rows of features
 // f .. f + 63, then the 64 up rows of the same features. A product tile then holds both halves of
@@ -176,21 +66,6 @@ template <int BN> struct SmallTile {
 // One tile (or one K range of a tile) per block, two blocks per SM, four warps that all join the
 // epilogue: for these short streams it starts and ends a few microseconds sooner than the
 // persistent kernel below.
-// What the epilogue for fused q/k/v projections (EPI 2) needs: a 128-row tile is one head of 128
-// dims there, and the block that owns a token norms, rotates and stores the head's row of it.
-struct HeadsEpilogue {
-  const float* q_norm_w;      // [128]
-  const float* k_norm_w;
-  const float* rope_table;    // [tokens][2][64]: cos, sin
-  const int* slot_map;        // [tokens]: page * page_tokens + slot
-  bf16* q_out;                // [tokens][q_heads][128]
-  bf16* k_pool;               // [pages][kv_heads][page_tokens][128]
-  bf16* v_pool;
-  int q_heads, kv_heads, page_tokens;
-  float eps;
-};
-__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-
 // CLUSTER: the `splits` blocks of a tile are one cluster (grid z = cluster z = splits, a power of
 // two). Block r owns rows r * 128 / splits .. of the tile: every block sends those rows of its
 // accumulator into r's shared memory, and after the cluster's barrier r adds them in split order
@@ -882,31 +757,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ------------------------------------------------------------------ host side
-PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) != cudaSuccess ||
-        status != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return (PFN_cuTensorMapEncodeTiled_v12000)p;
-  }();
-  return fn;
-}
-
-// rows x K bf16 matrix with row stride `ld` elements; box = 64 (K) x box_rows, 128-byte swizzle, zero fill
-bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
-  auto encode = encode_fn();
-  if (!encode) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // What the caller knows about the product; the launcher turns it into a schedule.
 struct Problem {
   int rows_a, rows_b, K, bn;

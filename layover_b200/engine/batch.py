@@ -28,6 +28,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, SequenceCache
@@ -185,34 +186,39 @@ class BatchBuilder:
             offset, _ = layout.fields[name]
             view[offset:offset + len(values)] = values
 
-        tokens_flat, positions, rows, row_slots, sources, cu = [], [], [], [], [], [0]
+        # per-token arrays are written as whole slices (a prompt portion has thousands of tokens)
+        ids_at, pos_at, src_at = (layout.fields[name][0] for name in ("token_ids", "positions", "token_src"))
+        rows, row_slots, cu = [], [], [0]
+        device_tokens = False
         for index, entry in enumerate(entries):
-            n = len(entry.tokens)
+            n, at = len(entry.tokens), cu[-1]
             for w in entry.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {entry.seq.request_id!r}: wanted place {w} is outside its {n} tokens")
-                rows.append(cu[-1] + w)
+                rows.append(at + w)
                 row_slots.append(entry.seq.slot)
-            tokens_flat.extend(entry.tokens)
-            sources.extend(entry.seq.slot if t < 0 else -1 for t in entry.tokens)
-            positions.extend(range(starts[index], starts[index] + n))
-            cu.append(cu[-1] + n)
+            view[ids_at + at: ids_at + at + n] = entry.tokens
+            view[pos_at + at: pos_at + at + n] = np.arange(starts[index], starts[index] + n, dtype=np.int32)
+            view[src_at + at: src_at + at + n] = -1
+            if n == 1 and entry.tokens[0] < 0:          # the request's newest token is in its record on the device
+                view[ids_at + at] = 0
+                view[src_at + at] = entry.seq.slot
+                device_tokens = True
+            cu.append(at + n)
         for _ in range(n_seqs - real):   # padding rows: token 0 at position 0 of the scratch page
-            tokens_flat.append(0); positions.append(0); sources.append(-1); cu.append(cu[-1] + 1)
+            at = cu[-1]
+            view[ids_at + at] = 0; view[pos_at + at] = 0; view[src_at + at] = -1
+            cu.append(at + 1)
         slots_of_seqs = [e.seq.slot for e in entries] + [cache.scratch_slot] * (n_seqs - real)
         if capacity:
             rows, row_slots = list(range(n_seqs)), slots_of_seqs
-        device_tokens = any(t < 0 for t in tokens_flat)
-        if device_tokens:
-            tokens_flat = [max(t, 0) for t in tokens_flat]
-        put("token_src", sources)
-        put("token_ids", tokens_flat); put("positions", positions); put("cu_q", cu); put("ctx_len", ctx_lens)
+        put("cu_q", cu); put("ctx_len", ctx_lens)
         put("state_slots", slots_of_seqs)
         put("logit_rows", rows); put("row_slots", row_slots)
         for g, group in enumerate(cache.paged):
             scratch = group.scratch_page
             offset, _ = layout.fields[f"table{g}"]
-            slots = []
+            slots_at = layout.fields[f"slots{g}"][0]
             for index in range(n_seqs):
                 row = view[offset + index * width: offset + (index + 1) * width]
                 row[:] = scratch
@@ -226,11 +232,10 @@ class BatchBuilder:
                             f"its table has {len(blocks)} and the batch is {width} wide")
                     row[:needed] = blocks[:needed]
                     cache.check_row(g, row[:needed], entry.seq.request_id)     # no bad page id reaches a kernel
-                    for pos in range(starts[index], ctx_lens[index]):
-                        slots.append(blocks[pos // page] * page + pos % page)
+                    where = np.arange(starts[index], ctx_lens[index], dtype=np.int64)
+                    view[slots_at + cu[index]: slots_at + cu[index + 1]] = row[where // page] * page + where % page
                 else:
-                    slots.append(scratch * page)
-            put(f"slots{g}", slots)
+                    view[slots_at + cu[index]] = scratch * page
         for size, tiles in tile_lists.items():
             put(f"tile_seq{size}", [t[0] for t in tiles]); put(f"tile_q0{size}", [t[1] for t in tiles])
         if mixed:

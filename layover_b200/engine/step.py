@@ -111,12 +111,13 @@ class StepFunction:
                 raise ValueError(f"request {seq.request_id!r}: state slot {seq.slot} is outside the cache")
             if seq.num_tokens + len(entry.tokens) > self.max_position:
                 raise ValueError(f"request {seq.request_id!r} would exceed {self.max_position} positions")
-            for token in entry.tokens:
-                if token == DEVICE_TOKEN:
-                    if len(entry.tokens) != 1:
-                        raise ValueError(f"request {seq.request_id!r}: a token still on the device comes alone")
-                elif not 0 <= token < self.vocab_size:
-                    raise ValueError(f"request {seq.request_id!r}: token {token} is outside the vocabulary")
+            low, high = min(entry.tokens), max(entry.tokens)
+            if low == DEVICE_TOKEN and len(entry.tokens) == 1:
+                continue
+            if low == DEVICE_TOKEN:
+                raise ValueError(f"request {seq.request_id!r}: a token still on the device comes alone")
+            if low < 0 or high >= self.vocab_size:
+                raise ValueError(f"request {seq.request_id!r}: token {low if low < 0 else high} is outside the vocabulary")
 
     def _reserve(self, entries: list[StepEntry]) -> None:
         """Pages for every entry or for none."""

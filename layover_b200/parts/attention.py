@@ -115,6 +115,13 @@ class Attention(Part):
 
     # ---- one step
     def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        q = self.project(h, batch, cache)
+        out = torch.empty_like(q)
+        self.attend(q, cache, batch, batch.groups[cache.group], out)
+        return self.runtime.linear(out, self.w_o)
+
+    def project(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        """q [T, q_heads * head_dim], normed and rotated; this step's keys and values go to their pages."""
         tokens = h.shape[0]
         own_kv = 0 if self.shares_cache else self.kv_heads
         group = batch.groups[cache.group]
@@ -127,9 +134,7 @@ class Attention(Part):
         if (heads is not None and own_kv and table is not None and self.qk_norm_eps is not None
                 and heads(h, self.w_qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, group.slot_map,
                           self.q_heads, own_kv, self.dim, cache.page_tokens, eps)):
-            out = torch.empty_like(q)      # projection, norm, rotation and page write were one kernel
-            self.attend(q, cache, batch, group, out)
-            return self.runtime.linear(out, self.w_o)
+            return q                       # projection, norm, rotation and page write were one kernel
         qkv = self.runtime.linear(h, self.w_qkv)
         if fused:
             ops.qk_norm_rope_kv(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, table, group.slot_map,
@@ -144,9 +149,7 @@ class Attention(Part):
             if own_kv:
                 ops.qk_norm_rope_kv(qkv, None, k_pool, v_pool, None, None, None, group.slot_map,
                                     self.q_heads, own_kv, self.dim, cache.page_tokens, eps)
-        out = torch.empty_like(q)
-        self.attend(q, cache, batch, group, out)
-        return self.runtime.linear(out, self.w_o)
+        return q
 
     def attend(self, q, cache, batch, group, out) -> None:
         self._attend(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.dim,

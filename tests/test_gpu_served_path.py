@@ -124,7 +124,7 @@ def test_engine_with_graphs_and_pipelining_at_the_served_head_size(tiny_folders)
 def layer_4b(tmp_path_factory):
     from safetensors.torch import load_file
 
-    config = lb.Qwen3Config(vocab_size=512, hidden_size=2560, intermediate_size=9728, num_hidden_layers=1,
+    config = lb.Qwen3Config(vocab_size=512, hidden_size=2560, intermediate_size=9728, num_hidden_layers=2,
                             num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=1024,
                             rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
     folder = tmp_path_factory.mktemp("layer-4b")
