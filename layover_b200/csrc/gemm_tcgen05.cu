@@ -911,6 +911,12 @@ LB_EXPORT void* lb_gemm_tcgen05_status_address() {
   return address;
 }
 
+// Writes the error word from the host: a drill for the path that reports a wait that ran out (a test
+// sets a code, runs a step and expects the engine to refuse the step's tokens and to recover).
+LB_EXPORT int lb_gemm_tcgen05_set_status(int code) {
+  return cudaMemcpyToSymbol(g_gemm_error, &code, sizeof(int)) == cudaSuccess ? 0 : -100;
+}
+
 // The error code a kernel recorded when one of its bounded waits ran out (0 = none); clears it.
 LB_EXPORT int lb_gemm_tcgen05_status() {
   int code = 0, zero = 0;

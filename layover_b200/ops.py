@@ -427,6 +427,16 @@ def gemm_status() -> int:
     return lib.lb_gemm_tcgen05_status()
 
 
+def gemm_set_status(code: int) -> None:
+    """Write the tensor-core product's error word from the host (a drill of the reporting path)."""
+    lib = build.load("gemm_tcgen05")
+    lib.lb_gemm_tcgen05_set_status.restype = c_int
+    lib.lb_gemm_tcgen05_set_status.argtypes = [c_int]
+    torch.cuda.synchronize()
+    if lib.lb_gemm_tcgen05_set_status(int(code)):
+        raise KernelError("gemm_tcgen05: cannot write the error word")
+
+
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T, bfloat16 operands, 32-bit accumulation; out bfloat16 or float32.
     Shapes that TMA cannot address (a row stride that is no multiple of 16 bytes) take the FFMA kernel."""

@@ -211,3 +211,32 @@ def test_a_corrupt_table_is_refused_before_any_launch(tiny_folders):
     logits = step([lb.StepEntry(seq, [5], [0])])          # and the cache still works
     assert logits.shape == (1, 256) and torch.isfinite(logits).all()
     cache.check()
+
+
+# ------------------------------------------------------------------ a kernel that gave up is heard of, and the engine recovers
+def test_a_wait_that_ran_out_reaches_the_host_with_the_tokens_and_the_engine_recovers(tiny_folders):
+    """Every wait in the tensor-core kernels is bounded; a wait that runs out leaves a code in the
+    library's error word and may leave split counters that are not back at zero. Nothing is made to
+    hang here: the test writes the code and dirty counters from the host, as such a kernel would leave
+    them. The sampling kernel carries the word to the host behind the step's tokens: the step's tokens
+    are refused with a KernelError, words and counters are put back, and generation goes on correctly."""
+    from layover_b200 import ops
+
+    folder, raw, weights = tiny_folders["c"]
+    model = lb.load_model(folder, device="cuda", dtype="bf16")
+    prompts = [random_prompt(384, n, 500 + n) for n in (12, 40)]
+    clean = lb.generate(model, prompts, max_new_tokens=6, block_tokens=16)
+    cache = lb.PagedKVCache(model, 32, block_tokens=16, max_requests=4)
+    engine = lb.Engine(model, cache, lb.EngineConfig(max_batch=2, prefill_chunk=64, prefill_budget=64))
+    for i, p in enumerate(prompts):
+        engine.add_request(lb.Request(str(i), p, 6))
+    engine.step()                                              # both prompts, first tokens
+    ops.gemm_set_status(4)                                     # "the split sum's wait ran out"
+    partials, counters, _ = ops.gemm_scratch(model.device)
+    counters[:8] = 3                                           # counters a block that gave up did not put back
+    with pytest.raises(ops.KernelError, match="gemm_tcgen05: code 4"):
+        engine.step()
+    assert ops.gemm_status() == 0 and int(counters.abs().sum()) == 0      # cleared before the error was raised
+    # a fresh engine on the same device runs the same requests to the same tokens
+    again = lb.generate(model, prompts, max_new_tokens=6, block_tokens=16)
+    assert again == clean
