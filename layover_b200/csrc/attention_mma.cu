@@ -62,25 +62,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-constexpr int TABLE_CACHE = 1024;   // block-table entries a block keeps in shared memory
+constexpr int TABLE_CACHE = 1024;   // block-table entries a prompt block keeps in shared memory
+constexpr int DECODE_TABLE_CACHE = 256;   // ... and a decode block (4,096 keys at pages of 16; the rest is read from global memory)
 
 // The pages of keys [first_key, last_key] copied to shared memory once, so that the tile loads do
 // not wait on a dependent global read each; entries past the cache are read from global memory.
 struct TableSlice {
   const int* table;
   const int* cached;
-  int first_page;
+  int first_page, capacity;
   __device__ __forceinline__ int page(int index) const {
     const int local = index - first_page;
-    return (local >= 0 && local < TABLE_CACHE) ? cached[local] : table[index];
+    return (local >= 0 && local < capacity) ? cached[local] : table[index];
   }
 };
 
-__device__ __forceinline__ TableSlice cache_table(int* cached, const int* __restrict__ table, int first_key,
+__device__ __forceinline__ TableSlice cache_table(int* cached, int capacity, const int* __restrict__ table, int first_key,
                                                    int last_key, int page_tokens) {
-  const int first_page = first_key / page_tokens, n = min(TABLE_CACHE, last_key / page_tokens - first_page + 1);
+  const int first_page = first_key / page_tokens, n = min(capacity, last_key / page_tokens - first_page + 1);
   for (int i = threadIdx.x; i < n; i += THREADS) cached[i] = table[first_page + i];
-  return TableSlice{table, cached, first_page};
+  return TableSlice{table, cached, first_page, capacity};
 }
 
 // Copies keys [tile * 64, +64) of one KV head into shared memory rows of (dim + PAD) bf16; keys
@@ -297,7 +298,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   const int p_first = start + q0, p_last = p_first + n_q - 1;
   const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
-  const TableSlice pages = cache_table(table_cache, table, key_lo, p_last, page_tokens);
+  const TableSlice pages = cache_table(table_cache, TABLE_CACHE, table, key_lo, p_last, page_tokens);
   const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
   __syncthreads();
 
@@ -381,15 +382,19 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 // block sends its partial values of a share to the share's owner and its maxima and sums to
 // everyone, through distributed shared memory; after a second barrier the owners add their shares
 // in split order and store them.
-template <int MAX_DIM, bool EXACT, bool UPPER, bool CLUSTER = false>
-__global__ void __launch_bounds__(THREADS)
+// STAGES: K/V tiles of a block in shared memory. Three keep a block's own stream going (two loads in
+// flight); with two a block is slower but three blocks share an SM instead of two, which wins once a
+// launch has more blocks than two per SM can hold at once (12 warps an SM hide the MMAs' latency
+// better than 8; measured at 64 sequences of 3,072 keys: 148 us against 158 us).
+template <int MAX_DIM, bool EXACT, bool UPPER, bool CLUSTER = false, int STAGES = 3>
+__global__ void __launch_bounds__(THREADS, STAGES == 2 ? 3 : 2)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         bf16* __restrict__ out, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                         const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim_arg, int page_tokens,
                         float scale_log2, int window, int splits, float* __restrict__ partials,
                         unsigned* __restrict__ counters, int chunk_shift, int page_shift) {
-  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, STAGES = 3;
+  constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int dim = EXACT ? MAX_DIM : dim_arg;
   const int stride = dim + PAD;
@@ -397,7 +402,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   bf16* k_s = q_s + 16 * stride;                          // [STAGES][BKEYS][stride]
   bf16* v_s = k_s + STAGES * BKEYS * stride;
   __shared__ unsigned last_flag;
-  __shared__ int table_cache[TABLE_CACHE];
+  __shared__ int table_cache[DECODE_TABLE_CACHE];
   // Lengths and block tables are written when the step begins, and the keys of earlier positions by
   // earlier steps: the block reads them, and requests its first tiles, while the kernel before it
   // still runs. What that kernel writes, the query and the tile that holds the newest key, is
@@ -418,7 +423,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const int per_split = (n_tiles + splits - 1) / splits;
   const int tile_begin = first_tile + split * per_split;
   const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
-  const TableSlice pages = cache_table(table_cache, table, max(key_lo, tile_begin * BKEYS),
+  const TableSlice pages = cache_table(table_cache, DECODE_TABLE_CACHE, table, max(key_lo, tile_begin * BKEYS),
                                        min(p, max(tile_end, tile_begin + 1) * BKEYS - 1), page_tokens);
   const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
   __syncthreads();
@@ -625,8 +630,8 @@ int exact_log2(int v) {
   return (1 << shift) == v ? shift : -1;
 }
 size_t prefill_smem(int dim) { return (size_t)(BQ + 4 * BKEYS) * (dim + PAD) * sizeof(bf16); }
-size_t decode_smem(int dim) {
-  const size_t tiles = (size_t)(16 + 2 * 3 * BKEYS) * (dim + PAD) * sizeof(bf16);
+size_t decode_smem(int dim, int stages = 3) {
+  const size_t tiles = (size_t)(16 + 2 * stages * BKEYS) * (dim + PAD) * sizeof(bf16);
   const size_t merge = (size_t)WARPS * 16 * (dim + 2) * sizeof(float);
   return tiles > merge ? tiles : merge;
 }
@@ -652,6 +657,8 @@ void configure_once() {      // once per device: the attribute belongs to the de
   allow_smem(attention_decode_kernel<256, false, true>, decode_smem(256));
   allow_smem(attention_decode_kernel<128, true, false, true>, decode_smem(128));
   allow_smem(attention_decode_kernel<128, true, true, true>, decode_smem(128));
+  allow_smem(attention_decode_kernel<128, true, false, false, 2>, decode_smem(128, 2));
+  allow_smem(attention_decode_kernel<128, true, false, true, 2>, decode_smem(128, 2));
 }
 
 // launches the decode kernel instantiation for this head size and group
@@ -711,13 +718,16 @@ LB_EXPORT long lb_attention_decode_scratch(int n_seqs, int q_heads, int dim, int
 }
 
 // Sequences with one new token each. `seq_list` (n_seqs indices into cu_q / ctx_len / block_table)
-// may be null for "all of them in order". A sequence whose ctx_len is 0 (no key at all) gets zeros. `counters` (n_seqs * kv_heads, zero between launches) and
+// may be null for "all of them in order". `stages` 2 asks for the variant with two K/V tiles a block in
+// shared memory and three blocks an SM (for launches of more blocks than two per SM hold at once); it
+// is honoured for head size 128 with at most 8 query heads per KV head, else three stages run. A sequence whose ctx_len is 0 (no key at all) gets zeros. `counters` (n_seqs * kv_heads, zero between launches) and
 // `partials` are needed when splits > 1.
 LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
                                        const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                        const int* seq_list, int n_seqs, int q_heads, int kv_heads, int dim,
                                        int page_tokens, float scale, int window, int splits, float* partials,
-                                       long partial_floats, unsigned* counters, int n_counters, cudaStream_t stream) {
+                                       long partial_floats, unsigned* counters, int n_counters, int stages,
+                                       cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads / kv_heads > 16 ||
       kv_heads > 65535 || splits < 1 || splits > 65535)
@@ -726,13 +736,26 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
                      (long)n_seqs * kv_heads > n_counters))
     return LB_ERR_SIZE;
   configure_once();
-  const size_t smem = decode_smem(dim);
+  // two K/V stages (three blocks an SM) exist for the served head size with at most 8 heads per KV head
+  const bool two_stages = stages == 2 && dim == 128 && q_heads / kv_heads <= 8;
+  const size_t smem = decode_smem(dim, two_stages ? 2 : 3);
   if ((3 * (size_t)splits + 1) * (q_heads / kv_heads) * sizeof(float) > smem) return LB_ERR_SIZE;   // merge factors
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_seqs, kv_heads, splits);
   int code;
-  if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
+  if (two_stages) {
+    if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
+      code = lb_launch_cluster(attention_decode_kernel<128, true, false, true, 2>, grid, dim3(THREADS), smem, stream, grid.z,
+                               (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width,
+                               cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits,
+                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift);
+    else
+      code = lb_launch(attention_decode_kernel<128, true, false, false, 2>, grid, dim3(THREADS), smem, stream, (const bf16*)q,
+                       (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
+                       q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
+                       page_shift);
+  } else if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
     code = launch_decode_cluster(q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                                  (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                                  q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, (float*)nullptr,

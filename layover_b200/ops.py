@@ -483,37 +483,51 @@ def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, t
     return out
 
 
-def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> int:
-    """How many ways to split the context of a decode step.
+def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> tuple[int, int]:
+    """(splits, stages): how many ways to split the context of a decode step, and which kernel variant.
 
-    A block is one (sequence, KV head, split), two blocks fit an SM, and the blocks run in rounds of
-    2 x SMs. With head size 128 the kernel runs 2, 4 or 8 splits as a thread-block cluster that merges
-    through distributed shared memory; more splits merge through scratch memory, which costs more.
-    The count is the one with the lowest estimate rounds x (64-key tiles per split + overhead in
-    tiles): 4 for a cluster, 10 for the scratch merge. That fits what was measured at 3,072 keys
-    (sequences: best splits) 1: 8, 4: 8, 8: 4, 16: 2, 24: 4, 32: 1, 40: 4, 48: 2, 64: 1, 128: 2, and one
-    sequence of 32,768 keys: 32 or more through scratch memory."""
+    A block is one (sequence, KV head, split). With three K/V tiles in shared memory two blocks fit an
+    SM; the variant with two tiles fits three (head size 128, at most 8 heads per KV head) but each
+    block is slower (about 1.15x per tile). Blocks run in rounds of blocks-per-SM x SMs. With head size
+    128 the kernel runs 2, 4 or 8 splits as a thread-block cluster that merges through distributed
+    shared memory; more splits merge through scratch memory, which costs more. The plan is the one
+    with the lowest estimate rounds x (64-key tiles per split + overhead in tiles): 4 for a cluster,
+    10 for the scratch merge. That fits what was measured at 3,072 keys (sequences: best splits)
+    1: 8, 4: 8, 8: 4, 16: 2, 24: 4, 32: 1, 40: 4, 48: 2, 128: 2, one sequence of 32,768 keys: 32 or
+    more through scratch memory, and 64 sequences: 4 splits with three blocks an SM (148 us against
+    158 us unsplit with two)."""
     natural = n_seqs * kv_heads
     want = max(1, 2 * sm_count // natural)                    # all blocks resident at once, two per SM
     splits = min(want, 128, max(1, max_context // 192))       # at least three 64-key tiles per split
     while splits > 1 and n_seqs * q_heads * splits * (dim + 2) > _ATTN_SCRATCH_FLOATS:
         splits -= 1
     if dim != 128:
-        return splits
-    slots, tiles = 2 * sm_count, max(1, -(-max_context // 64))
+        return splits, 3
+    tiles = max(1, -(-max_context // 64))
 
-    def estimate(count: int, overhead: int) -> int:
-        return -(-natural * count // slots) * (-(-tiles // count) + overhead)
+    def estimate(count: int, overhead: int, per_sm: int = 2, tile_cost: float = 1.0) -> float:
+        return -(-natural * count // (per_sm * sm_count)) * (-(-tiles // count) * tile_cost + overhead)
 
     best = min((c for c in (1, 2, 4, 8) if c <= tiles), key=lambda c: (estimate(c, 4), c))
-    if splits > 8 and estimate(splits, 10) < estimate(best, 4):
-        return splits
-    return best
+    plan, cost = (best, 3), estimate(best, 4)
+    if splits > 8 and estimate(splits, 10) < cost:
+        plan, cost = (splits, 3), estimate(splits, 10)
+    if natural > 2 * sm_count and q_heads // kv_heads <= 8:
+        # more blocks than two per SM hold at once: three slower blocks an SM may finish sooner
+        packed = min((c for c in (1, 2, 4, 8) if c <= tiles), key=lambda c: (estimate(c, 4, 3, 1.15), c))
+        if estimate(packed, 4, 3, 1.15) < cost:
+            plan = (packed, 2)
+    return plan
+
+
+def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> int:
+    return decode_plan(n_seqs, q_heads, kv_heads, dim, max_context, sm_count)[0]
 
 
 def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, seq_list, n_seqs, q_heads, kv_heads, dim,
-                          page_tokens, scale, window=0, splits=1):
-    """Tensor-core paged attention for sequences with one new token each, the context split `splits` ways."""
+                          page_tokens, scale, window=0, splits=1, stages=3):
+    """Tensor-core paged attention for sequences with one new token each, the context split `splits` ways
+    (`stages` 2: the variant that fits three blocks an SM, see `decode_plan`)."""
     for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
     for name, t in (("block_table", block_table), ("cu_q", cu_q), ("ctx_len", ctx_len)):
@@ -523,10 +537,10 @@ def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, se
     partials, counters = attention_scratch(q.device)
     fn = _fn("attention_mma", "lb_attention_decode_bf16",
              [c_void_p] * 5 + [c_int] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p, c_long, c_void_p,
-                                                                        c_int, c_void_p])
+                                                                        c_int, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
               _ptr(ctx_len), _ptr(seq_list), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale), int(window),
-              int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), _stream()),
+              int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), int(stages), _stream()),
            "attention_decode_bf16")
     return out
 
@@ -594,18 +608,18 @@ def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, pa
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
         # the widest context the block table can describe (what a captured step may later see)
-        splits = decode_splits(batch.n_seqs, q_heads, kv_heads, dim, block_table.shape[1] * page_tokens, sms)
+        splits, stages = decode_plan(batch.n_seqs, q_heads, kv_heads, dim, block_table.shape[1] * page_tokens, sms)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, None,
-                              batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits)
+                              batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages)
         return
     tiles_of = batch.tiles
     if batch.n_decode_seqs > 0 and q_heads // kv_heads <= 16:
         # a mixed step: the sequences with a single token go through the decode kernel (a tile kernel
         # would spend a whole tile of queries on each), the prompt portions through the tile kernel
         sms = gemm_scratch(q.device)[2]
-        splits = decode_splits(batch.n_decode_seqs, q_heads, kv_heads, dim, batch.decode_max_ctx, sms)
+        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, kv_heads, dim, batch.decode_max_ctx, sms)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, batch.decode_seqs,
-                              batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits)
+                              batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages)
         tiles_of = batch.portion_tiles
     if cache.pool is not None and attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens):
         tiles = tiles_of[TCGEN05_TILE]

@@ -459,6 +459,36 @@ def test_attention_decode_bf16_splits_as_clusters(q_heads, kv_heads, splits):
             close(got, expected, torch.bfloat16)
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 4])
+@pytest.mark.parametrize("q_heads, kv_heads", [(32, 8), (8, 1), (3, 3)])
+def test_attention_decode_bf16_with_two_stages(q_heads, kv_heads, splits):
+    """The variant with two K/V tiles a block in shared memory (three blocks an SM): the same results,
+    alone and with the splits as a cluster or through scratch memory, at page edges and short contexts."""
+    o = ops()
+    dim, page = 128, 16
+    lengths = [1, 63, 64, 65, 127, 129, 700, 1500, 16, 17]
+    k_pool, v_pool, table, ks, vs = paged_setup(torch.bfloat16, lengths, kv_heads, dim, page, seed=splits)
+    gen = torch.Generator().manual_seed(77)
+    qs = [torch.randn(1, q_heads, dim, generator=gen).to(torch.bfloat16) for _ in lengths]
+    q = torch.cat(qs).reshape(-1, q_heads * dim).cuda()
+    cu = torch.arange(len(lengths) + 1, dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    outs = []
+    for stages in (2, 3):
+        out = torch.full_like(q, float("nan"))
+        o.attention_decode_bf16(q, k_pool, v_pool, out, table, cu, ctx, None, len(lengths), q_heads, kv_heads, dim, page,
+                                1.0 / math.sqrt(dim), 0, splits, stages)
+        outs.append(out)
+    expected = []
+    for s, n in enumerate(lengths):
+        full_q = torch.zeros(n, q_heads, dim, dtype=torch.bfloat16)
+        full_q[-1:] = qs[s]
+        expected.append(plain_attention(full_q, ks[s], vs[s], None)[-1:])
+    assert not torch.isnan(outs[0]).any()
+    close(outs[0].cpu().view(-1, q_heads, dim), torch.cat(expected), torch.bfloat16)
+    assert torch.equal(outs[0], outs[1])          # the same tiles in the same order: the same bits as three stages
+
+
 @pytest.mark.parametrize("window", [1, 7, 64, 65, 300])
 def test_attention_decode_bf16_window(window):
     lengths = [1, 50, 64, 65, 300, 777]
