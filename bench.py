@@ -392,10 +392,11 @@ def kernel_points(model_name: str, pk: dict, with_library: bool) -> dict:
         o = torch.empty_like(q)
         cu = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
         lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
-        splits = ops.decode_splits(batch, nq, nkv, d, ctx, torch.cuda.get_device_properties(0).multi_processor_count)
+        splits, stages = ops.decode_plan(batch, nq, nkv, d, ctx, torch.cuda.get_device_properties(0).multi_processor_count)
         t = graph_time(lambda i: ops.attention_decode_bf16(q, pools[i % layers, 0], pools[i % layers, 1], o, table, cu, lens,
-                                                           None, batch, nq, nkv, d, page, 1 / math.sqrt(d), 0, splits), layers)
-        out[f"attn_decode_b{batch}"] = {"us": round(t * 1e3, 1), "splits": splits,
+                                                           None, batch, nq, nkv, d, page, 1 / math.sqrt(d), 0, splits, stages),
+                       layers)
+        out[f"attn_decode_b{batch}"] = {"us": round(t * 1e3, 1), "splits": splits, "stages": stages,
                                         "frac": round(batch * ctx * nkv * d * 4 / (t * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
         del pools
     # one prompt of 2,048 tokens through the prompt-portion attention (tcgen05 where it takes the sizes)

@@ -8,6 +8,10 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <functional>
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace {
@@ -153,17 +157,50 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// rows x K bf16 matrix with row stride `ld` elements; box = 64 (K) x box_rows, 128-byte swizzle, zero fill
+// rows x K bf16 matrix with row stride `ld` elements; box = 64 (K) x box_rows, 128-byte swizzle, zero fill.
+// Encoded maps are kept by (address, shape, stride, box): a weight's map is made once per process, and
+// an activation buffer that comes back at the same address (a captured step's, an allocator's reuse)
+// finds its map again. The table is small and guarded by one lock.
+struct MapKey {
+  const void* base;
+  long rows, K, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    h = h * 1000003u ^ std::hash<long>()(k.rows);
+    h = h * 1000003u ^ std::hash<long>()(k.K);
+    h = h * 1000003u ^ std::hash<long>()(k.ld);
+    return h * 1000003u ^ std::hash<int>()(k.box_rows);
+  }
+};
+
 bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
+  static std::mutex lock;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> known;
+  const MapKey key{base, rows, K, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = known.find(key);
+    if (found != known.end()) { *map = found->second; return true; }
+  }
   auto encode = encode_fn();
   if (!encode) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> guard(lock);
+  if (known.size() > 4096) known.clear();      // far more than a model's weights: start over rather than grow for ever
+  known.emplace(key, *map);
+  return true;
 }
-
 }  // namespace
