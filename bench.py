@@ -425,6 +425,51 @@ def kernel_points(model_name: str, pk: dict, with_library: bool) -> dict:
     return out
 
 
+def timeline_point(model, batch: int, gen) -> dict:
+    """Where a replayed decode step's time goes, kernel by kernel: a torch.profiler trace of three
+    replays at a context of 3,000 tokens; for one middle layer each kernel's own duration and the time
+    from the end of the kernel before it to its own end (kernels overlap under programmatic dependent
+    launch, so the second column is what a kernel adds to the step)."""
+    import re
+    import torch
+    import layover_b200 as lb
+    from layover_b200.engine.step import StepFunction
+    from torch.profiler import ProfilerActivity, profile
+
+    start = (PROMPT + CONTEXT) // 2 - 72
+    cache = lb.PagedKVCache(model, batch * (-(-(start + 64) // PAGE)), block_tokens=PAGE, max_requests=batch)
+    step_fn = StepFunction(model, cache, cuda_graphs=True, graph_sizes=(batch,), graph_max_tokens=CONTEXT)
+    seqs = fill_requests(step_fn, cache, batch, start, model.spec.vocab_size, gen)
+    entries = lambda: [lb.StepEntry(s, [5], [0]) for s in seqs]
+    for _ in range(5):
+        step_fn.sample(entries()).result()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step_fn.sample(entries()).result()
+        torch.cuda.synchronize()
+    events = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "memcpy" not in e.name.lower()]
+    events.sort(key=lambda e: e.time_range.start)
+
+    def short(name: str) -> str:
+        found = re.search(r"(\w+_kernel)(<[^>]*>)?", name)
+        return (found.group(1) + (found.group(2) or "")) if found else name[:60]
+
+    kernels = [(short(e.name), e.time_range.start, e.time_range.end) for e in events]
+    last = kernels[-(len(kernels) // 3):]
+    attention = [i for i, k in enumerate(last) if "attention_decode" in k[0]]
+    per_layer = attention[1] - attention[0]
+    middle = attention[len(attention) // 2]
+    rows, previous_end = [], last[middle - 1][2]
+    for name, begin, end in last[middle: middle + per_layer]:
+        rows.append({"kernel": name, "us": round(end - begin, 1), "adds_us": round(end - previous_end, 1)})
+        previous_end = end
+    ends = [last[i][2] for i in attention]
+    layers = [round(b - a, 1) for a, b in zip(ends, ends[1:])]
+    return {"only": "timeline", "batch": batch, "context": start + 8, "kernels_per_step": len(last), "kernels_per_layer": per_layer,
+            "layer_us": layers, "step_us": round(last[-1][2] - last[0][1], 1), "one_layer": rows}
+
+
 def run_4b(args, cfg, model, gen, pk, pk_source) -> dict:
     clocks = ClockSampler()
     check_graph_replay(model, gen)
@@ -593,6 +638,8 @@ def run_ours(args) -> dict:
         point = decode_point(model, args.batch, args.steps, args.warmup, gen)
         return {"only": "decode", "batch": args.batch, "layers_run": cfg.num_hidden_layers,
                 "tok_s": round(point["tok_s"], 1), "ms_per_step": round(point["ms_per_step"], 4)}
+    if args.only == "timeline":
+        return {"layers_run": cfg.num_hidden_layers, **timeline_point(model, args.batch, gen)}
     if args.only == "prefill":
         point = prefill_point(model, gen, repeats=max(1, args.steps))
         return {"only": "prefill", "layers_run": cfg.num_hidden_layers, "tok_s": round(point["tok_s"], 1),
@@ -727,9 +774,10 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the shape has (both numbers are reported)")
-    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
-                        help="decode or prefill alone, as a small target for a profiler, or the dominant kernels "
-                             "alone with cuBLAS beside them (prints a short line)")
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "timeline"],
+                        help="decode or prefill alone, as a small target for a profiler; the dominant kernels alone "
+                             "with cuBLAS beside them; or one replayed decode step's time kernel by kernel (each "
+                             "prints a short line)")
     args = parser.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
