@@ -249,13 +249,15 @@ def decode_point(model, batch: int, steps: int, warmup: int, gen, clocks=None, c
     return result
 
 
-def prefill_point(model, gen, repeats: int = 5) -> dict:
+def prefill_point(model, gen, repeats: int = 5, graphs: bool = True) -> dict:
+    """One prompt portion of PREFILL_TOKENS tokens, alone in its step, as the engine runs it: replayed
+    from a captured graph (`graphs`), or launch by launch."""
     import torch
     import layover_b200 as lb
     from layover_b200.engine.step import StepFunction
 
     cache = lb.PagedKVCache(model, PREFILL_TOKENS // PAGE + 1, block_tokens=PAGE, max_requests=2)
-    step_fn = StepFunction(model, cache)
+    step_fn = StepFunction(model, cache, cuda_graphs=graphs, portion_graph_tokens=(PREFILL_TOKENS,))
     ids = torch.randint(0, model.spec.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
     times = []
     for i in range(repeats + 2):
@@ -480,6 +482,7 @@ def run_4b(args, cfg, model, gen, pk, pk_source) -> dict:
                 for label, centre in ((PROMPT, PROMPT), ((PROMPT + CONTEXT) // 2, (PROMPT + CONTEXT) // 2),
                                       (CONTEXT, CONTEXT - few // 2 - 1))}
     prefill = prefill_point(model, gen)
+    prefill_eager = prefill_point(model, gen, graphs=False)
     points = {}
     for batch in (1, 64):
         points[f"decode_b{batch}"] = round(decode_point(model, batch, max(16, args.steps // 2), args.warmup, gen)["tok_s"], 1)
@@ -499,7 +502,8 @@ def run_4b(args, cfg, model, gen, pk, pk_source) -> dict:
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main["launches"],
         "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
-                    "frac": round(flops / (prefill["ms"] * 1e-3) / (tflops_peak * 1e12), 4)},
+                    "frac": round(flops / (prefill["ms"] * 1e-3) / (tflops_peak * 1e12), 4),
+                    "launch_by_launch_ms": round(prefill_eager["ms"], 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
@@ -642,8 +646,9 @@ def run_ours(args) -> dict:
         return {"layers_run": cfg.num_hidden_layers, **timeline_point(model, args.batch, gen)}
     if args.only == "prefill":
         point = prefill_point(model, gen, repeats=max(1, args.steps))
+        eager = prefill_point(model, gen, repeats=max(1, args.steps), graphs=False)
         return {"only": "prefill", "layers_run": cfg.num_hidden_layers, "tok_s": round(point["tok_s"], 1),
-                "ms": round(point["ms"], 3)}
+                "ms": round(point["ms"], 3), "launch_by_launch_ms": round(eager["ms"], 3)}
     runner = {"4b": run_4b, "4b-fp32": run_4b_fp32, "8b-mixed": run_8b_mixed, "32b-long": run_32b_long}[args.config]
     return runner(args, cfg, model, gen, pk, pk_source)
 

@@ -95,9 +95,17 @@ class StepBatch:
 
 @dataclass(frozen=True)
 class BatchCapacity:
-    """Fixed sizes of a batch whose buffers must not move (a captured decode step)."""
+    """Fixed sizes of a batch whose buffers must not move (a captured step). `portion == 0`: `seqs`
+    entries of one token each, every row's logits wanted, unused rows padded. `portion == N`: one
+    entry of exactly N tokens (a prompt portion), with the logits of its last token or none."""
     seqs: int
     table_width: int
+    portion: int = 0
+    want_last: bool = True
+
+    def __post_init__(self):
+        if self.portion and self.seqs != 1:
+            raise ValueError("a fixed-capacity prompt portion is a batch of one request")
 
 
 class _Layout:
@@ -147,16 +155,24 @@ class BatchBuilder:
         n_seqs = capacity.seqs if capacity else real
         if real > n_seqs:
             raise ValueError(f"{real} entries do not fit a batch of {n_seqs}")
-        q_lens = [len(e.tokens) for e in entries] + [1] * (n_seqs - real)
+        portion = capacity.portion if capacity else 0
+        q_lens = [len(e.tokens) for e in entries] + [portion or 1] * (n_seqs - real)
         if min(q_lens) < 1:
             raise ValueError("an entry without tokens")
         starts = [e.seq.num_tokens for e in entries] + [0] * (n_seqs - real)
         ctx_lens = [s + n for s, n in zip(starts, q_lens)]
         n_tokens = sum(q_lens)
-        if capacity and n_tokens != n_seqs:
-            raise ValueError("a fixed-capacity batch holds one token per entry")
+        if capacity and n_tokens != n_seqs * (portion or 1):
+            raise ValueError(f"a fixed-capacity batch holds {portion or 1} token(s) per entry")
         width = capacity.table_width if capacity else max(1, cache.blocks_for(max(ctx_lens)))
-        n_rows = sum(len(e.want) for e in entries) if not capacity else n_seqs
+        if not capacity:
+            n_rows = sum(len(e.want) for e in entries)
+        elif portion:
+            n_rows = 1 if capacity.want_last else 0
+            if entries and entries[0].want != ([portion - 1] if capacity.want_last else []):
+                raise ValueError("this fixed-capacity portion was made for other wanted places")
+        else:
+            n_rows = n_seqs
 
         layout = _Layout()
         layout.add("token_ids", n_tokens); layout.add("positions", n_tokens)
@@ -205,13 +221,17 @@ class BatchBuilder:
                 view[src_at + at] = entry.seq.slot
                 device_tokens = True
             cu.append(at + n)
-        for _ in range(n_seqs - real):   # padding rows: token 0 at position 0 of the scratch page
-            at = cu[-1]
-            view[ids_at + at] = 0; view[pos_at + at] = 0; view[src_at + at] = -1
-            cu.append(at + 1)
+        for _ in range(n_seqs - real):   # padding rows: token 0 from position 0 on, on the scratch page
+            at, n = cu[-1], portion or 1
+            view[ids_at + at: ids_at + at + n] = 0
+            view[pos_at + at: pos_at + at + n] = np.arange(n, dtype=np.int32)
+            view[src_at + at: src_at + at + n] = -1
+            cu.append(at + n)
         slots_of_seqs = [e.seq.slot for e in entries] + [cache.scratch_slot] * (n_seqs - real)
-        if capacity:
+        if capacity and not portion:
             rows, row_slots = list(range(n_seqs)), slots_of_seqs
+        elif capacity and not entries:
+            rows, row_slots = [portion - 1] * n_rows, [cache.scratch_slot] * n_rows
         put("cu_q", cu); put("ctx_len", ctx_lens)
         put("state_slots", slots_of_seqs)
         put("logit_rows", rows); put("row_slots", row_slots)
@@ -235,7 +255,8 @@ class BatchBuilder:
                     where = np.arange(starts[index], ctx_lens[index], dtype=np.int64)
                     view[slots_at + cu[index]: slots_at + cu[index + 1]] = row[where // page] * page + where % page
                 else:
-                    view[slots_at + cu[index]] = scratch * page
+                    where = np.arange(q_lens[index], dtype=np.int64)
+                    view[slots_at + cu[index]: slots_at + cu[index + 1]] = scratch * page + where % page
         for size, tiles in tile_lists.items():
             put(f"tile_seq{size}", [t[0] for t in tiles]); put(f"tile_q0{size}", [t[1] for t in tiles])
         if mixed:
@@ -283,7 +304,8 @@ class BatchBuilder:
         """Upper bound of the int32 words a fixed-capacity batch takes."""
         pad = lambda n: -(-max(n, 1) // 4) * 4
         s = capacity.seqs
-        total = 3 * pad(s) + pad(s + 1) + 4 * pad(s)
-        total += n_groups * (pad(s * capacity.table_width) + pad(s))
-        total += len(set(tile_sizes)) * 2 * pad(s)
+        t = s * (capacity.portion or 1)
+        total = 3 * pad(t) + pad(s + 1) + 4 * pad(s)
+        total += n_groups * (pad(s * capacity.table_width) + pad(t))
+        total += sum(2 * pad(s * -(-(capacity.portion or 1) // size)) for size in set(tile_sizes))
         return total

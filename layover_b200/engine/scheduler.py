@@ -123,7 +123,9 @@ class Engine:
         self.model, self.cache, self.config, self.clock = model, cache, config, clock
         if step_fn is None:
             from .step import StepFunction
-            step_fn = StepFunction(model, cache, cuda_graphs=cuda_graphs)
+            # a whole chunk of one prompt, alone in its step, is captured as well as the decode steps
+            step_fn = StepFunction(model, cache, cuda_graphs=cuda_graphs,
+                                   portion_graph_tokens=(config.prefill_chunk,) if cuda_graphs else ())
         self.step_fn = step_fn
         self.max_position = step_fn.max_position
         self.waiting: deque[Request] = deque()

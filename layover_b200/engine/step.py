@@ -14,6 +14,11 @@ address and unused rows padded onto the scratch page and the scratch record (the
 captures batch 1, 2, 4, 8 the same way, layover/decode_graphs.py:25-100). The width bucket is the
 request's pages rounded up to a power of two, so the attention's split count is planned for about
 the context that is really there, not for the longest a request could ever get.
+
+A step that is one prompt portion of a size named in `portion_graph_tokens` (the scheduler's
+prefill chunk) replays a graph too, one per (size, width bucket, last token's logits wanted or
+not): a portion is a few hundred launches, and the first short ones (embedding, norms, rotation)
+otherwise wait for the host between them.
 """
 
 from __future__ import annotations
@@ -30,18 +35,18 @@ DEFAULT_GRAPH_SIZES = (1, 2, 4, 8, 16, 32, 64)
 MIN_GRAPH_WIDTH = 64          # pages: the smallest block-table bucket a graph is captured for
 
 
-class _DecodeGraph:
-    """One captured decode step: `size` rows, tables `width` pages wide, with or without sampling."""
+class _CapturedStep:
+    """One captured step of fixed sizes (`capacity`), with or without sampling of its logit rows."""
 
-    def __init__(self, size: int, width: int, sampled: bool, step: "StepFunction"):
-        self.size, self.width, self.sampled = size, width, sampled
+    def __init__(self, capacity: BatchCapacity, sampled: bool, step: "StepFunction"):
+        self.capacity, self.sampled = capacity, sampled
+        self.size = (1 if capacity.want_last else 0) if capacity.portion else capacity.seqs   # logit rows
         cache = step.cache
-        self.capacity = BatchCapacity(size, width)
         words = BatchBuilder.buffer_size(self.capacity, len(cache.paged), step.builder.tile_sizes)
         self.buffer = torch.zeros(words, dtype=torch.int32, device=step.device)
         self.tokens = None
         if sampled:
-            self.tokens = torch.zeros(size + step.sampler.n_status, dtype=torch.int32, device=step.device)
+            self.tokens = torch.zeros(self.size + step.sampler.n_status, dtype=torch.int32, device=step.device)
         self.graph = None
         self.logits = None
         self.launches = 0
@@ -71,7 +76,7 @@ class _DecodeGraph:
 class StepFunction:
     def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False,
                  graph_sizes: tuple[int, ...] = DEFAULT_GRAPH_SIZES, graph_max_tokens: int | None = None,
-                 sampler: Sampler | None = None):
+                 sampler: Sampler | None = None, portion_graph_tokens: tuple[int, ...] = ()):
         self.model, self.cache = model, cache
         self.device = model.device
         self.builder = BatchBuilder(cache, self.device, model.tile_sizes())
@@ -83,12 +88,13 @@ class StepFunction:
         # a replay must reproduce bit for bit, which tests and the benchmark check)
         self.replay_graphs = True
         self.graph_sizes = tuple(sorted(s for s in graph_sizes if s <= cache.max_requests))
+        self.portion_graph_tokens = tuple(portion_graph_tokens)   # sizes of lone prompt portions to capture
         limit = graph_max_tokens or self.max_position
         self.graph_table_width = max(1, min(cache.blocks_for(limit), max(cache.num_blocks, 1)))
         if sampler is None:
             sampler = Sampler(self.device, cache.records, model.kernel_libraries(model.dtype))
         self.sampler = sampler
-        self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self._graphs: dict[tuple, _CapturedStep] = {}
         self._graph_pool = None
         self.steps = 0
         self.graph_replays = 0
@@ -160,7 +166,9 @@ class StepFunction:
                 else:
                     logits = graph._run(self, batch)
                 rows = [i for i, e in enumerate(entries) if e.want]
-                if sampled:
+                if sampled and graph.size == 0:
+                    out = PendingTokens(None, None, 0, 0, self.sampler)
+                elif sampled:
                     if len(rows) != len(entries):
                         raise ValueError("a replayed sampled step samples every row")     # _graph_for saw to it
                     out = self.sampler.collect(graph.tokens, len(entries), graph.size)
@@ -185,8 +193,12 @@ class StepFunction:
             width *= 2
         return min(width, self.graph_table_width)
 
-    def _graph_for(self, entries: list[StepEntry], sampled: bool) -> _DecodeGraph | None:
-        if not self.cuda_graphs or any(len(e.tokens) != 1 for e in entries):
+    def _graph_for(self, entries: list[StepEntry], sampled: bool) -> _CapturedStep | None:
+        if not self.cuda_graphs:
+            return None
+        if len(entries) == 1 and len(entries[0].tokens) in self.portion_graph_tokens and len(entries[0].tokens) > 1:
+            return self._portion_graph_for(entries[0], sampled)
+        if any(len(e.tokens) != 1 for e in entries):
             return None
         if any(e.want != [0] for e in entries) if sampled else any(e.want not in ([0], []) for e in entries):
             return None
@@ -201,8 +213,24 @@ class StepFunction:
             graph = self._capture(size, width, sampled)
         return graph
 
-    def _capture(self, size: int, width: int, sampled: bool) -> _DecodeGraph:
-        graph = _DecodeGraph(size, width, sampled, self)
+    def _portion_graph_for(self, entry: StepEntry, sampled: bool) -> _CapturedStep | None:
+        count = len(entry.tokens)
+        if entry.want not in ([], [count - 1]):
+            return None
+        width = self.graph_width_for(self.cache.blocks_for(entry.seq.num_tokens + count))
+        if width is None:
+            return None
+        want_last = bool(entry.want)
+        key = ("portion", count, width, want_last, sampled and want_last)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = _CapturedStep(BatchCapacity(1, width, count, want_last), sampled and want_last, self)
+            self._graph_pool = graph.capture(self, self._graph_pool)
+            self._graphs[key] = graph
+        return graph
+
+    def _capture(self, size: int, width: int, sampled: bool) -> _CapturedStep:
+        graph = _CapturedStep(BatchCapacity(size, width), sampled, self)
         self._graph_pool = graph.capture(self, self._graph_pool)
         self._graphs[(size, width, sampled)] = graph
         return graph

@@ -217,5 +217,46 @@ def test_fixed_capacity_batches_pad_onto_the_scratch_page():
     assert batch.groups[0].slot_map.tolist()[1:] == [scratch * 4] * 3
     assert batch.state_slots.tolist()[1:] == [m.scratch_slot] * 3
     assert batch.token_ids.data_ptr() == buffer.data_ptr()      # the descriptors sit at the fixed address
-    with pytest.raises(ValueError, match="one token per entry"):
+    with pytest.raises(ValueError, match=r"1 token\(s\) per entry"):
         BatchBuilder(m, "cpu").build([StepEntry(a, [3, 4], [0])], capacity, buffer)
+
+
+def test_a_fixed_capacity_prompt_portion():
+    """One request with exactly the capacity's tokens, at the fixed address, with the last token's
+    logits or none; with no request at all (what a capture runs) the tokens lie on the scratch page."""
+    m = manager([FULL], blocks=12, page=4, device="cpu")
+    a = m.open("a")
+    m.grow(a, 3); m.commit(a, 3); m.grow(a, 13)
+    capacity = BatchCapacity(1, 8, portion=10, want_last=True)
+    words = BatchBuilder.buffer_size(capacity, 1, (4, 16))
+    buffer = torch.zeros(words, dtype=torch.int32)
+    builder = BatchBuilder(m, "cpu", (4, 16))
+    tokens = list(range(20, 30))
+    batch = builder.build([StepEntry(a, tokens, [9])], capacity, buffer)
+    assert batch.n_tokens == 10 and batch.n_seqs == 1 and not batch.all_decode and batch.n_logit_rows == 1
+    assert batch.token_ids.tolist() == tokens and batch.positions.tolist() == list(range(3, 13))
+    assert batch.ctx_len.tolist() == [13] and batch.logit_rows.tolist() == [9] and batch.row_slots.tolist() == [a.slot]
+    assert batch.groups[0].block_table.shape == (1, 8)
+    blocks = a.tables[0].blocks
+    assert batch.groups[0].slot_map.tolist() == [blocks[p // 4] * 4 + p % 4 for p in range(3, 13)]
+    assert batch.tiles[4].count == 3 and batch.tiles[4].tile_q0.tolist() == [0, 4, 8] and batch.tiles[16].count == 1
+    assert batch.token_ids.data_ptr() == buffer.data_ptr()
+    layout_words = batch.tiles[16].tile_q0.data_ptr() - buffer.data_ptr()
+    assert layout_words // 4 + 4 <= words
+    # the same layout with nothing in it: every table entry and slot is the scratch page's
+    scratch = m.paged[0].scratch_page
+    empty = builder.build([], capacity, buffer)
+    assert empty.ctx_len.tolist() == [10] and empty.positions.tolist() == list(range(10))
+    assert set(empty.groups[0].block_table.flatten().tolist()) == {scratch}
+    assert all(slot // 4 == scratch for slot in empty.groups[0].slot_map.tolist())
+    assert empty.row_slots.tolist() == [m.scratch_slot] and empty.logit_rows.tolist() == [9]
+    assert empty.positions.data_ptr() == batch.positions.data_ptr()
+    # other sizes and other wanted places are refused
+    with pytest.raises(ValueError, match=r"10 token\(s\) per entry"):
+        builder.build([StepEntry(a, tokens[:9], [8])], capacity, buffer)
+    with pytest.raises(ValueError, match="other wanted places"):
+        builder.build([StepEntry(a, tokens, [])], capacity, buffer)
+    none_wanted = builder.build([StepEntry(a, tokens, [])], BatchCapacity(1, 8, portion=10, want_last=False), buffer)
+    assert none_wanted.n_logit_rows == 0
+    with pytest.raises(ValueError, match="batch of one request"):
+        BatchCapacity(2, 8, portion=10)

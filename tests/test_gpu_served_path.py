@@ -67,6 +67,46 @@ def test_a_replayed_step_equals_the_same_launches_without_a_graph(tiny_folders):
     assert torch.equal(records_a, records_b)
 
 
+@pytest.mark.parametrize("name,dtype_name", [("c", "bf16"), ("b", "fp32")])
+def test_a_captured_prompt_portion_equals_the_same_launches_without_a_graph(tiny_folders, name, dtype_name):
+    """A prompt cut into portions of the captured size (and a shorter rest): the portions replay a
+    graph, one that wants no logits and one that wants the last token's; logits, sampled token, cache
+    contents and record equal the same steps run launch by launch, and the plain implementation."""
+    from layover_b200.engine.step import StepFunction
+
+    folder, raw, weights = tiny_folders[name]
+    model = lb.load_model(folder, device="cuda", dtype=dtype_name)
+    page, size = TINY_PAGE[name], 48
+    vocab = raw["vocab_size"]
+    prompt = random_prompt(vocab, 3 * size + 11, 77)
+    outputs = []
+    for graphs in (True, False):
+        cache = lb.PagedKVCache(model, 4 * (len(prompt) // page + 2), block_tokens=page, max_requests=2)
+        step = StepFunction(model, cache, cuda_graphs=graphs, portion_graph_tokens=(size,))
+        got = []
+        for round_ in range(2):                       # the second request runs on pages and a graph used before
+            seq = cache.open(f"r{round_}")
+            step([lb.StepEntry(seq, prompt[:size], [])])
+            got.append(step([lb.StepEntry(seq, prompt[size:2 * size], [size - 1])]).clone().cpu())
+            tokens = step.sample([lb.StepEntry(seq, prompt[2 * size:3 * size], [size - 1])]).result()
+            got.append(step([lb.StepEntry(seq, prompt[3 * size:], [10])]).clone().cpu())
+            got.append(torch.tensor(tokens))
+            if round_ == 0:
+                cache.close(seq)
+        assert step.graph_replays == (6 if graphs else 0)
+        outputs.append((got, cache.records[: cache.max_requests].cpu().clone()))    # not the scratch record
+    (with_graph, records_a), (without, records_b) = outputs
+    for a, b in zip(with_graph, without):
+        assert torch.equal(a, b)
+    assert torch.equal(records_a, records_b)
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    plain = plain_forward(raw, weights, prompt, dtype)
+    for got_row, place in ((with_graph[0][0], 2 * size - 1), (with_graph[1][0], len(prompt) - 1)):
+        assert (got_row - plain[place]).abs().max() <= tolerance(plain[place], dtype)
+    token, row = int(with_graph[2][0]), plain[3 * size - 1]
+    assert row[token] >= row.max() - tolerance(row, dtype)
+
+
 # ------------------------------------------------------------------ many requests decoding together
 @pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])
 @pytest.mark.parametrize("count", [24, 64, 130])
