@@ -163,10 +163,10 @@ __device__ __forceinline__ void lb_cluster_barrier() {    // every thread of eve
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// A launch with the blocks of one z column as a thread-block cluster of `cluster_z` blocks.
+// A launch with thread-block clusters of `cluster` blocks (every dimension divides the grid's).
 template <typename... KArgs, typename... Args>
-static inline int lb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    unsigned cluster_z, Args... args) {
+static inline int lb_launch_cluster_dims(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                         dim3 cluster, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -174,12 +174,19 @@ static inline int lb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   config.stream = stream;
   cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
-  attribute[0].val.clusterDim.x = 1;
-  attribute[0].val.clusterDim.y = 1;
-  attribute[0].val.clusterDim.z = cluster_z;
+  attribute[0].val.clusterDim.x = cluster.x;
+  attribute[0].val.clusterDim.y = cluster.y;
+  attribute[0].val.clusterDim.z = cluster.z;
   attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = lb_pdl_enabled() ? 2 : 1;
   return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
+// A launch with the blocks of one z column as a thread-block cluster of `cluster_z` blocks.
+template <typename... KArgs, typename... Args>
+static inline int lb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    unsigned cluster_z, Args... args) {
+  return lb_launch_cluster_dims(kernel, grid, block, smem, stream, dim3(1, 1, cluster_z), args...);
 }

@@ -397,16 +397,20 @@ gemm_fewtoken_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 // ------------------------------------------------------------------ the persistent kernel
 // The few-token orientation asks for two blocks per SM (half the shared memory each): a weight
 // matrix with about as many tiles as SMs then still runs in one round.
-template <int BN, bool SWAP> struct Tile {
+// PAIR: two blocks of a cluster work as one MMA unit on a tile of 256 rows x BN columns; each block
+// stages its own 128 rows and its own half of the BN columns' operand, a third fewer bytes into
+// each SM per product than a block on its own, and so more stages in the same memory.
+template <int BN, bool SWAP, bool PAIR = false> struct Tile {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BLOCKS_PER_SM = SWAP ? 2 : 1;
-  static constexpr int BUDGET = SMEM_BUDGET / BLOCKS_PER_SM;
+  static constexpr int BUDGET = SMEM_BUDGET / BLOCKS_PER_SM;   // a pair's seventh stage fits in 227 KB, and measured no faster
   static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
   static constexpr int ACC_COLS = BN < 16 ? 16 : BN;          // columns of one accumulator
   static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ +
+                              (PAIR ? 1024 : 0) /* norm weights of the q/k/v epilogue */;
 };
 
 // How the output tiles are dealt to the blocks. Tiles are numbered with the 128-row side fastest.
@@ -441,16 +445,30 @@ __device__ __forceinline__ Segment segment_at(const Schedule& sch, int block, in
 
 constexpr int EPILOGUE_WARPS = 4;
 constexpr int PERSISTENT_THREADS = (2 + EPILOGUE_WARPS) * 32;
+// the q/k/v epilogue (EPI 2) does more per value, so two warps share each quarter of the accumulator's
+// lanes, one per head of the tile
+__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 2 ? 2 * EPILOGUE_WARPS : EPILOGUE_WARPS; }
+__host__ __device__ constexpr int persistent_threads(int epi) { return (2 + epilogue_warps(epi)) * 32; }
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // D[i, j] = sum_k Aop[i, k] Bop[j, k], i on the 128-row side. SWAP false: C[i, j] = D; true: C[j, i] = D.
-template <int BN, bool SWAP, typename OutT, int EPI>
-__global__ void __launch_bounds__(PERSISTENT_THREADS, Tile<BN, SWAP>::BLOCKS_PER_SM)
+// PAIR (never with SWAP): the grid is clusters of two blocks along x. What the schedule calls a block
+// is a pair, and a tile has 256 rows: block `rank` of the pair stages rows 128 rank .. of the A side
+// and rows BN / 2 * rank .. of the B side, all copies report to the leader's `full` barriers, the
+// leader (rank 0) issues MMAs of M = 256 whose commits arrive on the `empty` and `acc_full` barriers
+// of both blocks, both blocks' epilogues arrive on the leader's `acc_empty`, and each block's
+// epilogue handles its own 128 rows like a tile of its own (with a scratch slot of its own when K
+// is split).
+template <int BN, bool SWAP, typename OutT, int EPI, bool PAIR = false>
+__global__ void __launch_bounds__(persistent_threads(EPI), Tile<BN, SWAP, PAIR>::BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OutT* __restrict__ C, long ldc, int rows_a, int rows_b, const Schedule sch,
-                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok) {
-  using T = Tile<BN, SWAP>;
+                    float* __restrict__ partials, unsigned* __restrict__ counters, bool vector_ok, const HeadsEpilogue he) {
+  static_assert(!(PAIR && SWAP), "pairs of blocks serve the many-token orientation");
+  static_assert(EPI != 2 || (PAIR && BN == 256 && sizeof(OutT) == 2), "the q/k/v epilogue takes a pair's 256-column tiles of bfloat16");
+  using T = Tile<BN, SWAP, PAIR>;
+  constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles_a = smem;
@@ -461,26 +479,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* acc_empty = acc_full + 2;         // [2] the epilogue has read an accumulator
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* flag = tmem_slot + 1;    // [0] a wait ran out, [1] this block is the last of its tile
+  float* norm_w = reinterpret_cast<float*>(smem + T::STAGES * T::STAGE_BYTES + 256);   // EPI 2: [2][128] q and k norm weights
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int block = blockIdx.x, blocks = gridDim.x;
+  const int rank = PAIR ? (int)lb_cluster_rank() : 0;                // 0: the block that issues the MMAs
+  const int block = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int blocks = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int n_segments = segment_count(sch, block);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPILOGUE_WARPS); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], (PAIR ? 2 : 1) * epilogue_warps(EPI)); }
     flag[0] = 0; flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, T::TMEM_COLS);
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair(tmem_slot, T::TMEM_COLS);
+    else tmem_alloc(tmem_slot, T::TMEM_COLS);
+  }
+  if (EPI == 2) {      // weights, which no kernel writes: no need to wait for the kernel before
+    for (int i = threadIdx.x; i < 2 * BM; i += blockDim.x) norm_w[i] = i < BM ? he.q_norm_w[i] : he.k_norm_w[i - BM];
+  }
   fence_before_sync();
-  __syncthreads();
+  if (PAIR) lb_cluster_barrier();      // neither block signals the other's barriers before they exist
+  else __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
 
-  if (warp == 0) {
+  if (PAIR && warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer of a pair: this block's rows of both operands, reported to the leader
+      const uint32_t leader_full = lb_map_to_rank(smem_u32(full), 0);
+      pdl_wait();
+      int it = 0;
+      for (int j = 0; j < n_segments && !flag[0]; ++j) {
+        const Segment seg = segment_at(sch, block, blocks, j);
+        const int m0 = (seg.tile % sch.tiles_m) * TILE_ROWS + rank * BM;
+        const int n0 = (seg.tile / sch.tiles_m) * BN + rank * (BN / 2);
+        for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
+          const int s = it % T::STAGES;
+          const uint32_t phase = (it / T::STAGES) & 1;
+          if (it >= T::STAGES && !mbar_wait(&empty[s], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 1); flag[0] = 1; break; }
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * T::STAGE_BYTES);
+          tma_load_2d_pair(tiles_a + s * T::A_BYTES, &map_a, leader_full + 8u * s, kb * BK, m0);
+          tma_load_2d_pair(tiles_b + s * T::B_BYTES, &map_b, leader_full + 8u * s, kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 0) {
     if (lane == 0) {
       // ---------------- producer. Weights are written by no kernel, so the first ring of weight
       // tiles is requested before waiting for the kernel that produces the activations.
@@ -531,9 +579,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       // ---------------- MMA issuer
-      constexpr uint32_t idesc = instr_desc(BN);
+      constexpr uint32_t idesc = instr_desc(BN, TILE_ROWS);
       int it = 0;
       for (int j = 0; j < n_segments && !flag[0]; ++j) {
         const Segment seg = segment_at(sch, block, blocks, j);
@@ -548,12 +596,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           fence_after_sync();
           const uint64_t a_desc = smem_desc(tiles_a + s * T::A_BYTES), b_desc = smem_desc(tiles_b + s * T::B_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)   // +32 bytes per K step inside the swizzled row
-            umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > seg.kb_begin || k > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);
+          for (int k = 0; k < BK / UMMA_K; ++k) {  // +32 bytes per K step inside the swizzled row
+            if (PAIR) umma_bf16_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > seg.kb_begin || k > 0) ? 1u : 0u);
+            else umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > seg.kb_begin || k > 0) ? 1u : 0u);
+          }
+          if (PAIR) umma_commit_pair(&empty[s], 3);
+          else umma_commit(&empty[s]);
         }
         if (flag[0]) break;
-        umma_commit(&acc_full[buf]);
+        if (PAIR) umma_commit_pair(&acc_full[buf], 3);
+        else umma_commit(&acc_full[buf]);
       }
     }
   } else {
@@ -563,14 +615,98 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     pdl_wait();   // the stores below touch memory that earlier kernels may still be reading
     for (int j = 0; j < n_segments; ++j) {
       const Segment seg = segment_at(sch, block, blocks, j);
-      const int m0 = (seg.tile % sch.tiles_m) * BM, n0 = (seg.tile / sch.tiles_m) * BN;
+      const int m0 = (seg.tile % sch.tiles_m) * TILE_ROWS + rank * BM, n0 = (seg.tile / sch.tiles_m) * BN;
       const int buf = j & 1;
       if (!mbar_wait(&acc_full[buf], (j >> 1) & 1)) { atomicCAS(&g_gemm_error, 0, 3); flag[0] = 1; break; }
       fence_after_sync();
       const uint32_t lane_base = tmem_base + buf * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       const int valid_cols = min(BN, rows_b - n0);
-      const int slot = seg.tile - sch.full * blocks;         // index among the last round's tiles
+      // index among the last round's tiles; each block of a pair has a partial tile of its own
+      const int slot = PAIR ? 2 * (seg.tile - sch.full * blocks) + rank : seg.tile - sch.full * blocks;
       float* my_partial = seg.splits > 1 ? partials + ((size_t)slot * seg.splits + seg.split) * BN * BM : nullptr;
+      if (EPI == 2) {
+        // The fused q/k/v projection (never split along K): the tile's 256 columns are two heads of
+        // 128, one for each of the two warps that share this quarter of the lanes, and this thread
+        // holds one token's row of its head. It does what the per-head norm kernel does, every
+        // rounding in the same place and the sum of squares in the same order (that kernel's eight
+        // lanes of eight (low, high) pairs, then its butterfly), so the bits agree: RMSNorm and
+        // rotation of q and k heads, q to its buffer, k and v to their page. The accumulator is read
+        // twice (sum, then values) instead of keeping 128 values in registers.
+        const int token = m0 + row;
+        const bool live = token < rows_a;
+        const int half = (warp - 2) >> 2;
+        if (half * 128 < valid_cols) {
+          const int head = (n0 >> 7) + half;
+          const bool is_q = head < he.q_heads, is_k = !is_q && head < he.q_heads + he.kv_heads;
+          const float* w = is_q ? norm_w : (is_k ? norm_w + BM : nullptr);
+          const uint32_t col0 = lane_base + half * 128;
+          float inv = 0.f;
+          if (w) {
+            float part[8];
+#pragma unroll
+            for (int c = 0; c < 64; c += 16) {
+              float lo[16], hi[16];
+              tmem_ld16_two(col0 + c, col0 + 64 + c, lo, hi);
+#pragma unroll
+              for (int g = 0; g < 2; ++g) {
+                float ss = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) ss += lb_square_pair(round_bf16(lo[8 * g + jj]), round_bf16(hi[8 * g + jj]));
+                part[(c >> 3) + g] = ss;
+              }
+            }
+            const float ss = ((part[0] + part[4]) + (part[2] + part[6])) + ((part[1] + part[5]) + (part[3] + part[7]));
+            inv = 1.0f / sqrtf(ss / (float)BM + he.eps);
+          }
+          bf16* dst = nullptr;
+          if (live) {
+            if (is_q) {
+              dst = he.q_out + ((size_t)token * he.q_heads + head) * BM;
+            } else {
+              const int slot_id = he.slot_map[token];
+              const int kvh = is_k ? head - he.q_heads : head - he.q_heads - he.kv_heads;
+              const size_t page = slot_id / he.page_tokens, within = slot_id % he.page_tokens;
+              dst = (is_k ? he.k_pool : he.v_pool) + ((page * he.kv_heads + kvh) * he.page_tokens + within) * BM;
+            }
+          }
+          const float* cos_row = he.rope_table + (size_t)(live ? token : 0) * 2 * 64;
+#pragma unroll
+          for (int c = 0; c < 64; c += 16) {
+            float4 cs4[4], sn4[4];
+            if (w) {       // asked for before the accumulator's values, so that both are on their way together
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                cs4[i] = __ldg(reinterpret_cast<const float4*>(cos_row + c) + i);
+                sn4[i] = __ldg(reinterpret_cast<const float4*>(cos_row + 64 + c) + i);
+              }
+            }
+            float lo[16], hi[16];
+            tmem_ld16_two(col0 + c, col0 + 64 + c, lo, hi);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { lo[i] = round_bf16(lo[i]); hi[i] = round_bf16(hi[i]); }   // the projection's own rounding
+            if (w) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float cs[4] = {cs4[i].x, cs4[i].y, cs4[i].z, cs4[i].w}, sn[4] = {sn4[i].x, sn4[i].y, sn4[i].z, sn4[i].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int d = 4 * i + e;
+                  const float yl = round_bf16(w[c + d] * round_bf16(lo[d] * inv));
+                  const float yh = round_bf16(w[64 + c + d] * round_bf16(hi[d] * inv));
+                  const float cc = round_bf16(cs[e]), sv = round_bf16(sn[e]);
+                  // rotate_half(x) = (-hi, lo): each product and the sum round to bfloat16
+                  lo[d] = round_bf16(round_bf16(yl * cc) + round_bf16(-yh * sv));
+                  hi[d] = round_bf16(round_bf16(yh * cc) + round_bf16(yl * sv));
+                }
+              }
+            }
+            if (dst) {
+              store_row16<bf16>(dst + c, lo);
+              store_row16<bf16>(dst + 64 + c, hi);
+            }
+          }
+        }
+      }
       if (EPI == 1 && seg.splits == 1) {
         // columns come as [64 gate | 64 up] per 128: one thread holds both halves of its token's
         // features and writes 64 activations per 128 columns
@@ -594,7 +730,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      for (int c = 0; c < BN && !(EPI == 1 && seg.splits == 1); c += 16) {
+      for (int c = 0; c < BN && !(EPI == 1 && seg.splits == 1) && EPI != 2; c += 16) {
         if (c >= valid_cols) break;                           // uniform over the block
         float v[16];
         tmem_ld16(lane_base + c, v);
@@ -626,7 +762,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // the accumulator may be overwritten now
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(lb_map_to_rank(smem_u32(&acc_empty[buf]), 0));
+        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+      }
 
       if (seg.splits > 1) {
         // Every block of the tile adds up its own share of the columns, over all splits in split
@@ -750,9 +889,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if (PAIR) lb_cluster_barrier();       // the other block may still signal this one's barriers until here
   if (warp == 1) {
     fence_after_sync();
-    tmem_dealloc(tmem_base, T::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, T::TMEM_COLS);
+    else tmem_dealloc(tmem_base, T::TMEM_COLS);
   }
 }
 
@@ -824,7 +965,83 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc
   }
   float* partials = sch.last_splits > 1 ? pb.scratch : nullptr;
   const int code = lb_launch(kernel, dim3(blocks), dim3(PERSISTENT_THREADS), (size_t)T::SMEM, stream, map_a, map_b,
-                             (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials, pb.counters, vector_ok);
+                             (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials, pb.counters, vector_ok, HeadsEpilogue{});
+  return code ? code : lb_last_error();
+}
+
+// The many-token product on pairs of blocks (`cta_group::2`), tiles of 256 tokens x 256 weight rows.
+// Returns -1 when this GPU holds no cluster of two such blocks (nothing is launched then).
+// LAYOVER_B200_GEMM_PAIR=0 keeps every product on single blocks.
+static inline bool lb_gemm_pair_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("LAYOVER_B200_GEMM_PAIR");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
+
+template <typename OutT, int EPI = 0>
+int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, long ldc, const Problem& pb, bool vector_ok,
+                cudaStream_t stream, const HeadsEpilogue& he = HeadsEpilogue{}) {
+  constexpr int BN = 256;
+  using T = Tile<BN, false, true>;
+  auto kernel = gemm_tcgen05_kernel<BN, false, OutT, EPI, true>;
+  static int pairs_resident = 0;      // clusters of two that the GPU holds at once (the same on every B200)
+  static LbPerDeviceOnce configured;
+  if (configured.first()) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM) != cudaSuccess)
+      return lb_last_error();
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(2 * pb.sm_count);
+    probe.blockDim = dim3(persistent_threads(EPI));
+    probe.dynamicSmemBytes = T::SMEM;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;       // the two blocks of an MMA pair are neighbours along x
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    probe.attrs = attribute;
+    probe.numAttrs = 1;
+    int fit = 0;
+    if (cudaOccupancyMaxActiveClusters(&fit, kernel, &probe) != cudaSuccess) { cudaGetLastError(); fit = 0; }
+    pairs_resident = fit;
+  }
+  // Blocks that split a tile wait for one another, so a launch never has more pairs than the GPU
+  // holds at once.
+  const int slots = pairs_resident < pb.sm_count / 2 ? pairs_resident : pb.sm_count / 2;
+  if (slots < 1) return -1;
+  Schedule sch;
+  sch.tiles_m = (pb.rows_a + 2 * BM - 1) / (2 * BM);
+  sch.tiles = sch.tiles_m * ((pb.rows_b + BN - 1) / BN);
+  sch.total_kb = (pb.K + BK - 1) / BK;
+  int cap = pb.max_splits > 0 ? pb.max_splits : 8;
+  if (!pb.scratch || !pb.counters || EPI == 2) cap = 1;      // the q/k/v epilogue needs whole sums in one place
+  int pairs;
+  if (sch.tiles >= slots) {
+    pairs = slots;
+    sch.full = sch.tiles / pairs;
+    sch.rem = sch.tiles % pairs;
+  } else {
+    pairs = sch.tiles;
+    sch.full = 0;
+    sch.rem = sch.tiles;
+  }
+  sch.last_splits = 1;
+  if (sch.rem > 0) {
+    int splits = slots / sch.rem;
+    if (splits > cap) splits = cap;
+    if (splits > sch.total_kb / 4) splits = sch.total_kb / 4;       // at least four K blocks per split
+    const long per_split = (long)sch.rem * 2 * BN * BM;              // each block of a pair has a partial tile
+    if (splits > 1 && per_split * splits > pb.scratch_floats) splits = (int)(pb.scratch_floats / per_split);
+    if (splits > 1 && 4 * sch.rem > pb.n_counters) splits = 1;
+    if (splits < 1) splits = 1;
+    sch.last_splits = splits;
+    if (sch.full == 0) pairs = sch.rem * splits;
+  }
+  float* partials = sch.last_splits > 1 ? pb.scratch : nullptr;
+  const int code = lb_launch_cluster_dims(kernel, dim3(2 * pairs), dim3(persistent_threads(EPI)), (size_t)T::SMEM, stream,
+                                          dim3(2, 1, 1), map_a, map_b, (OutT*)C, ldc, pb.rows_a, pb.rows_b, sch, partials,
+                                          pb.counters, vector_ok, he);
   return code ? code : lb_last_error();
 }
 
@@ -961,6 +1178,17 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
   const Problem pb{rows_a, rows_b, K, bn, swap, sm_count, max_splits, scratch, scratch_floats, counters, n_counters};
   const int elem = out_dtype == LB_BF16 ? 2 : 4;
   const bool vector_ok = ((uintptr_t)C % 16 == 0) && ((ldc * elem) % 16 == 0);
+  // Prompt portions of 512 tokens and more on 256-wide weights: pairs of blocks on tiles of 256 x 256
+  if (!swap && bn == 256 && M >= 512 && lb_gemm_pair_enabled()) {
+    CUtensorMap map_half;
+    if (make_map(&map_half, W, N, K, ldw, 128)) {
+      int code;
+      if (epilogue == 1) code = launch_pair<bf16, 1>(map_a, map_half, C, ldc, pb, vector_ok, stream);
+      else if (out_dtype == LB_BF16) code = launch_pair<bf16>(map_a, map_half, C, ldc, pb, vector_ok, stream);
+      else code = launch_pair<float>(map_a, map_half, C, ldc, pb, vector_ok, stream);
+      if (code != -1) return code;
+    }
+  }
 #define LB_GEMM_CASE(BN_, SWAP_)                                                                       \
   if (bn == BN_ && swap == SWAP_) {                                                                    \
     if (out_dtype == LB_BF16) return launch<BN_, SWAP_, bf16>(map_a, map_b, C, ldc, pb, vector_ok, stream); \
@@ -1007,23 +1235,34 @@ LB_EXPORT int lb_gemm_tcgen05(const void* A, const void* W, void* C, int out_dty
   return LB_ERR_SIZE;
 }
 
-// The q/k/v projection of `M` <= 16 tokens fused with the per-head norm, the rotation and the page
+// The q/k/v projection of `M` tokens fused with the per-head norm, the rotation and the page
 // write: W [(q_heads + 2 kv_heads) * 128, K] stacked q, k, v; what `lb_gemm_tcgen05` followed by the
-// per-head norm kernel would leave in q_out and the pools, bit for bit. Returns 0 when launched,
-// 1 when these sizes are not taken (head size other than 128, more than 16 tokens, too few K blocks
-// to split, clusters switched off): nothing has been launched then.
+// per-head norm kernel would leave in q_out and the pools, bit for bit. Up to 16 tokens run in the
+// few-token kernel (clusters along K), 512 and more on pairs of blocks (a thread of the epilogue
+// holds a token's whole head). Returns 0 when launched, 1 when these sizes are not taken (head size
+// other than 128, 17..511 tokens, too few K blocks to split, clusters or pairs switched off):
+// nothing has been launched then.
 LB_EXPORT int lb_gemm_qkv_heads(const void* A, const void* W, int M, int K, long lda, long ldw, int q_heads, int kv_heads,
                                 int head_dim, const float* q_norm_w, const float* k_norm_w, const float* rope_table,
                                 int n_freq, const int* slot_map, void* q_out, void* k_pool, void* v_pool, int page_tokens,
                                 float eps, int sm_count, cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (head_dim != BM || M > 16 || n_freq * 2 != head_dim || !q_norm_w || !k_norm_w || !rope_table || !slot_map || !q_out ||
-      !k_pool || !v_pool || q_heads < 1 || kv_heads < 1 || page_tokens < 1)
+  if (head_dim != BM || (M > 16 && M < 512) || n_freq * 2 != head_dim || !q_norm_w || !k_norm_w || !rope_table ||
+      !slot_map || !q_out || !k_pool || !v_pool || q_heads < 1 || kv_heads < 1 || page_tokens < 1)
     return 1;
   if (!lb_gemm_tcgen05_supports(A, W, K, lda, ldw)) return 1;
   if (sm_count < 1) sm_count = 1;
   const int rows = (q_heads + 2 * kv_heads) * head_dim;
   CUtensorMap map_a, map_b;
+  if (M >= 512) {
+    if (!lb_gemm_pair_enabled() || rows <= 128) return 1;
+    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_b, W, rows, K, ldw, 128)) return 1;
+    const Problem many{M, rows, K, 256, false, sm_count, 1, nullptr, 0, nullptr, 0};
+    const HeadsEpilogue he{q_norm_w, k_norm_w, rope_table, slot_map, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool,
+                           q_heads, kv_heads, page_tokens, eps};
+    const int code = launch_pair<bf16, 2>(map_a, map_b, nullptr, 0L, many, false, stream, he);
+    return code == -1 ? 1 : code;
+  }
   if (!make_map(&map_a, W, rows, K, ldw, BM) || !make_map(&map_b, A, M, K, lda, 16)) return 1;
   const Problem pb{rows, M, K, 16, true, sm_count, 0, nullptr, 0, nullptr, 0};
   const HeadsEpilogue he{q_norm_w, k_norm_w, rope_table, slot_map, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool,

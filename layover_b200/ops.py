@@ -389,12 +389,12 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, max_splits
 def gemm_qkv_heads(h: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                    q_norm_w: torch.Tensor, k_norm_w: torch.Tensor, table: torch.Tensor, slot_map: torch.Tensor,
                    q_heads: int, kv_heads: int, dim: int, page_tokens: int, eps: float) -> bool:
-    """The stacked q/k/v projection of up to 16 tokens with the per-head norm, the rotation and the
-    page write in its epilogue (head size 128): leaves in q_out and the pools what `gemm_tcgen05`
-    followed by `qk_norm_rope_kv` leaves there, bit for bit. False: these sizes are not taken and
-    nothing was launched."""
+    """The stacked q/k/v projection of up to 16 tokens, or of 512 and more, with the per-head norm, the
+    rotation and the page write in its epilogue (head size 128): leaves in q_out and the pools what
+    `gemm_tcgen05` followed by `qk_norm_rope_kv` leaves there, bit for bit. False: these sizes are not
+    taken and nothing was launched."""
     tokens = h.shape[0]
-    if (dim != 128 or tokens > 16 or h.dtype != torch.bfloat16 or q_norm_w is None or k_norm_w is None or table is None
+    if (dim != 128 or 16 < tokens < 512 or h.dtype != torch.bfloat16 or q_norm_w is None or k_norm_w is None or table is None
             or k_pool is None or not gemm_tcgen05_supports(h, w_qkv)):
         return False
     for name, t in (("h", h), ("w_qkv", w_qkv), ("q_out", q_out), ("k_pool", k_pool), ("v_pool", v_pool)):

@@ -381,6 +381,9 @@ def test_sampling_follows_the_distribution():
 @pytest.mark.parametrize("m, n, k", [
     (1, 96, 64), (8, 2560, 4096), (16, 6144, 2560), (17, 200, 96), (33, 1000, 200), (64, 2560, 9728), (100, 392, 136),
     (128, 256, 64), (129, 96, 64), (300, 200, 96), (2048, 640, 2560), (257, 1000, 264), (5, 8, 8), (8, 151936, 64),
+    # 512 tokens and more on wide weights: pairs of blocks on tiles of 256 x 256 (whole tiles, ragged
+    # edges on both sides, a last round split along K, several rounds)
+    (512, 256, 64), (513, 300, 136), (1000, 2560, 4096), (2048, 6144, 2560), (700, 520, 264), (4096, 10240, 512),
 ])
 def test_gemm_tcgen05(out_dtype, m, n, k):
     o = ops()
@@ -519,13 +522,14 @@ def test_bf16_attention_finds_one_far_key_among_thousands(kernel, far_key):
     assert (out.float().cpu() - 7.0).abs().max() < 0.05
 
 
-@pytest.mark.parametrize("tokens", [1, 3, 8, 16])
+@pytest.mark.parametrize("tokens", [1, 3, 8, 16, 512, 700, 2048])
 @pytest.mark.parametrize("q_heads, kv_heads, hidden", [(32, 8, 2560), (4, 2, 1024), (3, 1, 512), (16, 8, 1024)])
 def test_fused_qkv_projection_equals_product_then_head_kernel(q_heads, kv_heads, hidden, tokens):
     """The q/k/v projection with norm, rotation and page write in its epilogue leaves the same bits in
-    the query buffer and the pages as the product followed by the per-head kernel."""
+    the query buffer and the pages as the product followed by the per-head kernel: the few-token
+    kernel up to 16 tokens, pairs of blocks from 512 on (an odd number of heads leaves half a tile)."""
     o = ops()
-    dim, page, pages = 128, 16, 9
+    dim, page, pages = 128, 16, max(9, tokens // 16 + 3)
     gen = torch.Generator().manual_seed(tokens * 1000 + q_heads)
     rows = (q_heads + 2 * kv_heads) * dim
     h = torch.randn(tokens, hidden, generator=gen).to(torch.bfloat16).cuda()
@@ -544,7 +548,7 @@ def test_fused_qkv_projection_equals_product_then_head_kernel(q_heads, kv_heads,
 
     k1, v1 = pools()
     qkv = torch.empty(tokens, rows, dtype=torch.bfloat16, device="cuda")
-    o.gemm_tcgen05(h, w, qkv)
+    o.gemm_tcgen05(h, w, qkv, max_splits=1 if tokens >= 512 else 0)     # the fused many-token product never splits K
     q1 = torch.empty(tokens, q_heads * dim, dtype=torch.bfloat16, device="cuda")
     o.qk_norm_rope_kv(qkv, q1, k1, v1, q_w, k_w, table, slots, q_heads, kv_heads, dim, page, 1e-6)
     k2, v2 = pools()
@@ -553,8 +557,11 @@ def test_fused_qkv_projection_equals_product_then_head_kernel(q_heads, kv_heads,
         taken = o.gemm_qkv_heads(h, w, q2, k2, v2, q_w, k_w, table, slots, q_heads, kv_heads, dim, page, 1e-6)
     assert o.gemm_status() == 0
     if not taken:
-        # too few K blocks to split, nothing to split for, or clusters switched off for the run
-        assert hidden // 64 < 8 or rows // 128 >= 148 or os.environ.get("LAYOVER_B200_CLUSTER_REDUCE") == "0"
+        # too few K blocks to split, nothing to split for, or clusters (pairs) switched off for the run
+        if tokens >= 512:
+            assert os.environ.get("LAYOVER_B200_GEMM_PAIR") == "0"
+        else:
+            assert hidden // 64 < 8 or rows // 128 >= 148 or os.environ.get("LAYOVER_B200_CLUSTER_REDUCE") == "0"
         return
     assert torch.equal(q1, q2)
     assert torch.equal(k1, k2) and torch.equal(v1, v2)

@@ -194,6 +194,53 @@ def test_every_cut_at_the_4b_layer_shape(layer_4b, tmp_path, dtype_name):
                         assert np.array_equal(rows[rid][position], row), f"{cut}: {rid} position {position} differs"
 
 
+def test_long_portions_at_the_4b_layer_shape(layer_4b, tmp_path):
+    """Portions of 512 tokens and more take the products on pairs of blocks and the q/k/v projection
+    with the norm, the rotation and the page write in its epilogue; shorter ones the single-block
+    products and the per-head kernel. A 900-token prompt whole, as 600 + 300 and as three times 300,
+    and 600 of it beside two other requests' single tokens: the wanted rows against the plain
+    implementation, and the three cuts against one another."""
+    folder, raw, weights, _ = layer_4b
+    long = random_prompt(512, 900, 4242)
+    short = {"s0": random_prompt(512, 20, 1), "s1": random_prompt(512, 35, 2)}
+    wanted = [0, 1, 299, 300, 511, 512, 599, 600, 898, 899]
+
+    def cut(sizes):
+        steps, at = [], 0
+        for size in sizes:
+            want = [w - at for w in wanted if at <= w < at + size]
+            steps.append({"entries": [{"id": "long", "tokens": long[at:at + size], "want": want}], "end": []})
+            at += size
+        steps[-1]["end"] = ["long"]
+        return [dict(step, step=i) for i, step in enumerate(steps)]
+
+    beside = [{"step": 0, "entries": [{"id": rid, "tokens": tokens[:-1], "want": []} for rid, tokens in short.items()], "end": []},
+              {"step": 1, "entries": [{"id": "long", "tokens": long[:600], "want": [w for w in wanted if w < 600]}] +
+                                     [{"id": rid, "tokens": tokens[-1:], "want": [0]} for rid, tokens in short.items()],
+               "end": ["s0", "s1"]},
+              {"step": 2, "entries": [{"id": "long", "tokens": long[600:], "want": [w - 600 for w in wanted if w >= 600]}],
+               "end": ["long"]}]
+    plain = plain_forward(raw, weights, long, torch.bfloat16)
+    expected = {"long": plain.numpy()}
+    expected.update({rid: plain_forward(raw, weights, tokens, torch.bfloat16).numpy() for rid, tokens in short.items()})
+    results = {}
+    for name, steps in (("whole", cut([900])), ("600+300", cut([600, 300])), ("3x300", cut([300, 300, 300])), ("beside", beside)):
+        rows = run_trace(folder, "bfloat16", steps, tmp_path / name, block_tokens=16, max_tokens=1100)
+        assert sorted(rows["long"]) == wanted
+        for rid, got in rows.items():
+            bound = tolerance(torch.from_numpy(expected[rid]), torch.bfloat16)
+            for position, row in got.items():
+                worst = np.abs(row - expected[rid][position]).max()
+                assert worst <= bound, f"{name}: {rid} position {position}: |diff| {worst:.3e} > {bound:.3e}"
+        if name == "beside":
+            assert sorted(rows["s0"]) == [19] and sorted(rows["s1"]) == [34]
+        results[name] = rows["long"]
+    bound = tolerance(plain, torch.bfloat16)
+    for name in ("600+300", "3x300", "beside"):
+        for position in wanted:
+            assert np.abs(results[name][position] - results["whole"][position]).max() <= bound
+
+
 # ------------------------------------------------------------------ a checkpoint stored in 32-bit, run in bfloat16
 def test_a_32bit_checkpoint_run_in_bfloat16(tmp_path):
     """Every floating tensor is rounded to the run's dtype when it is loaded, the norm weights too
