@@ -657,6 +657,10 @@ void configure_once() {      // once per device: the attribute belongs to the de
   allow_smem(attention_decode_kernel<256, false, true>, decode_smem(256));
   allow_smem(attention_decode_kernel<128, true, false, true>, decode_smem(128));
   allow_smem(attention_decode_kernel<128, true, true, true>, decode_smem(128));
+  // clusters of 16 blocks (one sequence's context cut 16 ways) are beyond the portable size of 8
+  cudaFuncSetAttribute(attention_decode_kernel<128, true, false, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  cudaFuncSetAttribute(attention_decode_kernel<128, true, true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  cudaGetLastError();
   allow_smem(attention_decode_kernel<128, true, false, false, 2>, decode_smem(128, 2));
   allow_smem(attention_decode_kernel<128, true, false, true, 2>, decode_smem(128, 2));
 }
@@ -676,7 +680,7 @@ int launch_decode(int dim, int group, dim3 grid, size_t smem, cudaStream_t strea
 // Whether the splits of this launch can run as clusters: head size 128, 2, 4 or 8 splits, and room
 // for the received shares behind the warps' merge area.
 bool decode_cluster_fits(int dim, int group, int splits, size_t smem) {
-  if (dim != 128 || splits < 2 || splits > 8 || (splits & (splits - 1)) || !lb_cluster_reduce_enabled()) return false;
+  if (dim != 128 || splits < 2 || splits > 16 || (splits & (splits - 1)) || !lb_cluster_reduce_enabled()) return false;
   const size_t per = ((size_t)group * dim + splits - 1) / splits;
   const size_t need = ((size_t)WARPS * 16 * (dim + 2) + splits * per + (size_t)splits * group * 2) * sizeof(float);
   return need <= smem;

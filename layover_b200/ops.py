@@ -490,7 +490,9 @@ def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context:
     SM; the variant with two tiles fits three (head size 128, at most 8 heads per KV head) but each
     block is slower (about 1.15x per tile). Blocks run in rounds of blocks-per-SM x SMs. With head size
     128 the kernel runs 2, 4 or 8 splits as a thread-block cluster that merges through distributed
-    shared memory; more splits merge through scratch memory, which costs more. The plan is the one
+    shared memory (16 where all the launch's blocks still fit one per SM: a single sequence, 8.7
+    against 10.6 us at 3,072 keys; two sequences 16.5 against 12.1 us, so not there); more splits merge
+    through scratch memory, which costs more. The plan is the one
     with the lowest estimate rounds x (64-key tiles per split + overhead in tiles): 4 for a cluster,
     10 for the scratch merge. That fits what was measured at 3,072 keys (sequences: best splits)
     1: 8, 4: 8, 8: 4, 16: 2, 24: 4, 32: 1, 40: 4, 48: 2, 128: 2, one sequence of 32,768 keys: 32 or
@@ -508,7 +510,10 @@ def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context:
     def estimate(count: int, overhead: int, per_sm: int = 2, tile_cost: float = 1.0) -> float:
         return -(-natural * count // (per_sm * sm_count)) * (-(-tiles // count) * tile_cost + overhead)
 
-    best = min((c for c in (1, 2, 4, 8) if c <= tiles), key=lambda c: (estimate(c, 4), c))
+    clustered = [c for c in (1, 2, 4, 8) if c <= tiles]
+    if 16 <= tiles // 3 and natural * 16 <= sm_count:
+        clustered.append(16)
+    best = min(clustered, key=lambda c: (estimate(c, 4), c))
     plan, cost = (best, 3), estimate(best, 4)
     if splits > 8 and estimate(splits, 10) < cost:
         plan, cost = (splits, 3), estimate(splits, 10)
