@@ -21,6 +21,10 @@
 //     Whole rounds of tiles are dealt one tile per block; the tiles left over are split along K so
 //     that the last round keeps every SM busy, and the blocks of a tile then add up the partial
 //     tiles together, each its share of the columns, in split order.
+//     From 512 tokens on the same kernel runs on PAIRS of blocks (clusters of two, cta_group::2):
+//     a pair takes tiles of 256 tokens x 256 weight rows, each block stages half of either operand
+//     and keeps the accumulator rows of its own 128 tokens; the q/k/v projection of 128-dim heads
+//     then also norms, rotates and stores the heads in its epilogue.
 //   few tokens: one tile (or one K range of a tile) per block of four warps, two blocks per SM; the
 //     block that arrives last at the tile's counter adds the partial tiles in split order.
 // Every wait (on an mbarrier, or on sibling blocks) is bounded: when a limit runs out the block
