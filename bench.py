@@ -552,7 +552,7 @@ def run_8b_mixed(args, cfg, model, gen, pk, pk_source) -> dict:
     cache = lb.PagedKVCache(model, pages, block_tokens=PAGE, max_requests=requests)
     engine = lb.Engine(model, cache, lb.EngineConfig(requests, chunk, chunk), cuda_graphs=True)
     # graphs are captured before the clock starts
-    engine.step_fn.capture_all(tokens=max(lengths) + new_tokens, from_tokens=min(lengths))
+    engine.step_fn.capture_all(tokens=max(lengths) + new_tokens, from_tokens=min(lengths), skews=(1, 2))
     for i, n in enumerate(lengths):
         engine.add_request(lb.Request(str(i), torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist(), new_tokens))
     clocks = ClockSampler()

@@ -90,6 +90,10 @@ class StepBatch:
     max_ctx: int
     all_decode: bool
     real_seqs: int = 0          # entries that are not padding
+    # the longest and the mean context of the sequences with a single token, as the decode attention
+    # is to plan for them (a captured step: of the class of steps it is captured for)
+    plan_max_ctx: int = 0
+    plan_mean_ctx: int = 0
     shared: dict = field(default_factory=dict)   # what parts make once per step and share (rotary tables)
 
 
@@ -147,7 +151,7 @@ class BatchBuilder:
         return buffer[:size], index
 
     def build(self, entries: list[StepEntry], capacity: BatchCapacity | None = None,
-              device_buffer: torch.Tensor | None = None) -> StepBatch:
+              device_buffer: torch.Tensor | None = None, plan_ctx: tuple[int, int] | None = None) -> StepBatch:
         cache, page = self.cache, self.cache.block_tokens
         if not entries and capacity is None:
             raise ValueError("a step needs at least one entry")
@@ -297,6 +301,8 @@ class BatchBuilder:
                            for size, tiles in portion_lists.items()},
             q_lens=q_lens, ctx_lens=ctx_lens, max_q_len=max(q_lens), max_ctx=max(ctx_lens),
             all_decode=max(q_lens) == 1, real_seqs=real,
+            plan_max_ctx=plan_ctx[0] if plan_ctx else max((ctx_lens[s] for s in singles), default=0),
+            plan_mean_ctx=plan_ctx[1] if plan_ctx else (sum(ctx_lens[s] for s in singles) // len(singles) if singles else 0),
         )
 
     @staticmethod

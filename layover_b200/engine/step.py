@@ -38,8 +38,9 @@ MIN_GRAPH_WIDTH = 64          # pages: the smallest block-table bucket a graph i
 class _CapturedStep:
     """One captured step of fixed sizes (`capacity`), with or without sampling of its logit rows."""
 
-    def __init__(self, capacity: BatchCapacity, sampled: bool, step: "StepFunction"):
+    def __init__(self, capacity: BatchCapacity, sampled: bool, step: "StepFunction", plan_ctx: tuple[int, int] | None = None):
         self.capacity, self.sampled = capacity, sampled
+        self.plan_ctx = plan_ctx      # (longest, mean) context that the decode attention of this graph is planned for
         self.size = (1 if capacity.want_last else 0) if capacity.portion else capacity.seqs   # logit rows
         cache = step.cache
         words = BatchBuilder.buffer_size(self.capacity, len(cache.paged), step.builder.tile_sizes)
@@ -58,7 +59,7 @@ class _CapturedStep:
         return logits
 
     def capture(self, step: "StepFunction", pool):
-        batch = step.builder.build([], self.capacity, self.buffer)   # padding rows only
+        batch = step.builder.build([], self.capacity, self.buffer, self.plan_ctx)   # padding rows only
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -157,7 +158,7 @@ class StepFunction:
         with profiling.nvtx_range("step"):
             graph = self._graph_for(entries, sampled)
             if graph is not None:
-                batch = self.builder.build(entries, graph.capacity, graph.buffer)
+                batch = self.builder.build(entries, graph.capacity, graph.buffer, graph.plan_ctx)
                 if self.replay_graphs:
                     graph.graph.replay()
                     logits = graph.logits
@@ -205,12 +206,14 @@ class StepFunction:
         size = next((s for s in self.graph_sizes if s >= len(entries)), None)
         if size is None:
             return None
-        width = self.graph_width_for(max(self.cache.blocks_for(e.seq.num_tokens + 1) for e in entries))
+        lengths = [e.seq.num_tokens + 1 for e in entries]
+        width = self.graph_width_for(self.cache.blocks_for(max(lengths)))
         if width is None:
             return None
-        graph = self._graphs.get((size, width, sampled))
+        skew = 2 if 2 * max(lengths) * len(lengths) > 3 * sum(lengths) else 1     # the longest is 1.5 times the mean or more
+        graph = self._graphs.get((size, width, sampled, skew))
         if graph is None:
-            graph = self._capture(size, width, sampled)
+            graph = self._capture(size, width, sampled, skew)
         return graph
 
     def _portion_graph_for(self, entry: StepEntry, sampled: bool) -> _CapturedStep | None:
@@ -229,13 +232,17 @@ class StepFunction:
             self._graphs[key] = graph
         return graph
 
-    def _capture(self, size: int, width: int, sampled: bool) -> _CapturedStep:
-        graph = _CapturedStep(BatchCapacity(size, width), sampled, self)
+    def _capture(self, size: int, width: int, sampled: bool, skew: int = 1) -> _CapturedStep:
+        """`skew` 1: a step whose requests are about equally long; 2: one whose longest request has 1.5
+        times the mean or more (the decode attention cuts the contexts further for those)."""
+        longest = width * self.cache.block_tokens
+        graph = _CapturedStep(BatchCapacity(size, width), sampled, self, (longest, longest // skew))
         self._graph_pool = graph.capture(self, self._graph_pool)
-        self._graphs[(size, width, sampled)] = graph
+        self._graphs[(size, width, sampled, skew)] = graph
         return graph
 
-    def capture_all(self, tokens: int | None = None, sampled: bool = True, from_tokens: int | None = None) -> None:
+    def capture_all(self, tokens: int | None = None, sampled: bool = True, from_tokens: int | None = None,
+                    skews: tuple[int, ...] = (1,)) -> None:
         """Capture now, instead of at first use, every batch-size bucket for requests that hold between
         `from_tokens` (default: `tokens`) and `tokens` tokens (default: the widest table): every
         block-table bucket in that range, largest first so that the smaller ones fit in its memory pool."""
@@ -246,5 +253,6 @@ class StepFunction:
         widths = sorted({w for w in (self.graph_width_for(p) for p in range(low, top + 1)) if w is not None}, reverse=True)
         for width in widths:
             for size in reversed(self.graph_sizes):
-                if (size, width, sampled) not in self._graphs:
-                    self._capture(size, width, sampled)
+                for skew in skews:
+                    if (size, width, sampled, skew) not in self._graphs:
+                        self._capture(size, width, sampled, skew)

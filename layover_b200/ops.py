@@ -483,7 +483,8 @@ def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, t
     return out
 
 
-def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int) -> tuple[int, int]:
+def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context: int, sm_count: int,
+                mean_context: int | None = None) -> tuple[int, int]:
     """(splits, stages): how many ways to split the context of a decode step, and which kernel variant.
 
     A block is one (sequence, KV head, split). With three K/V tiles in shared memory two blocks fit an
@@ -497,7 +498,14 @@ def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context:
     10 for the scratch merge. That fits what was measured at 3,072 keys (sequences: best splits)
     1: 8, 4: 8, 8: 4, 16: 2, 24: 4, 32: 1, 40: 4, 48: 2, 128: 2, one sequence of 32,768 keys: 32 or
     more through scratch memory, and 64 sequences: 4 splits with three blocks an SM (148 us against
-    158 us unsplit with two)."""
+    158 us unsplit with two).
+
+    `mean_context`: the sequences' mean length where it is known to be well below the longest (more
+    than 1.5 times). The longest sequence's blocks then run on alone at a lone block's rate after the
+    others have finished, so the context is cut further, into about 7 blocks an SM (at least 12 tiles
+    each), with three blocks an SM as soon as two do not hold them all. Measured with lengths spread
+    evenly over 0.1..1 of 8,192 keys (us, the plan for equal lengths against this one): 8 sequences
+    54 -> 47, 16: 106 -> 80, 32: 219 -> 136; over 0.1..1 of 3,072 keys: 16: 41 -> 36, 32: 79 -> 56."""
     natural = n_seqs * kv_heads
     want = max(1, 2 * sm_count // natural)                    # all blocks resident at once, two per SM
     splits = min(want, 128, max(1, max_context // 192))       # at least three 64-key tiles per split
@@ -517,6 +525,15 @@ def decode_plan(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_context:
     plan, cost = (best, 3), estimate(best, 4)
     if splits > 8 and estimate(splits, 10) < cost:
         plan, cost = (splits, 3), estimate(splits, 10)
+    skewed = mean_context is not None and 2 * max_context > 3 * max(1, mean_context)
+    if skewed and q_heads // kv_heads <= 8 and 8 * natural > 2 * sm_count and 10 * natural < 34 * sm_count:
+        count = 1
+        while count < 8 and 2 * count * count * natural * natural <= (7 * sm_count) ** 2:   # nearest power of two to 7 SMs / natural
+            count *= 2
+        while count > 1 and tiles // count < 12:
+            count //= 2
+        if count >= 2:
+            return (count, 3) if natural * count <= 2 * sm_count else (count, 2)
     if natural > 2 * sm_count and q_heads // kv_heads <= 8:
         # more blocks than two per SM hold at once: three slower blocks an SM may finish sooner
         packed = min((c for c in (1, 2, 4, 8) if c <= tiles), key=lambda c: (estimate(c, 4, 3, 1.15), c))
@@ -612,8 +629,10 @@ def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, pa
     one; single tokens, alone or beside prompt portions, go through the split decode kernel."""
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
-        # the widest context the block table can describe (what a captured step may later see)
-        splits, stages = decode_plan(batch.n_seqs, q_heads, kv_heads, dim, block_table.shape[1] * page_tokens, sms)
+        # planned for the step's own lengths; a captured step for its class of steps (the widest context
+        # its block table can describe, with the mean that the class stands for)
+        widest = min(batch.plan_max_ctx or block_table.shape[1] * page_tokens, block_table.shape[1] * page_tokens)
+        splits, stages = decode_plan(batch.n_seqs, q_heads, kv_heads, dim, widest, sms, batch.plan_mean_ctx or None)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, None,
                               batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages)
         return
@@ -622,7 +641,8 @@ def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, pa
         # a mixed step: the sequences with a single token go through the decode kernel (a tile kernel
         # would spend a whole tile of queries on each), the prompt portions through the tile kernel
         sms = gemm_scratch(q.device)[2]
-        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, kv_heads, dim, batch.decode_max_ctx, sms)
+        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, kv_heads, dim, batch.decode_max_ctx, sms,
+                                     batch.plan_mean_ctx or None)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, batch.decode_seqs,
                               batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages)
         tiles_of = batch.portion_tiles
