@@ -529,7 +529,9 @@ def test_fused_qkv_projection_equals_product_then_head_kernel(q_heads, kv_heads,
     the query buffer and the pages as the product followed by the per-head kernel: the few-token
     kernel up to 16 tokens, pairs of blocks from 512 on (an odd number of heads leaves half a tile)."""
     o = ops()
-    dim, page, pages = 128, 16, max(9, tokens // 16 + 3)
+    dim = 128
+    page = {32: 16, 4: 32, 3: 8, 16: 64}[q_heads]           # pages of other sizes than the engine's usual 16 too
+    pages = max(9, tokens // page + 3)
     gen = torch.Generator().manual_seed(tokens * 1000 + q_heads)
     rows = (q_heads + 2 * kv_heads) * dim
     h = torch.randn(tokens, hidden, generator=gen).to(torch.bfloat16).cuda()
