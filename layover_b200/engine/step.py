@@ -9,7 +9,8 @@ batch. `sample(entries)` does the same and then chooses a token for every wanted
 device (`sampling.Sampler`), returning them on their way to the host.
 
 A step of single tokens only (every live request decoding) can replay a captured CUDA graph: one
-graph per (batch size bucket, block-table width bucket), with the batch's descriptors at a fixed
+graph per (batch size bucket, block-table width bucket, requests about equally long or not: the
+decode attention plans its launch differently for the two), with the batch's descriptors at a fixed
 address and unused rows padded onto the scratch page and the scratch record (the reference
 captures batch 1, 2, 4, 8 the same way, layover/decode_graphs.py:25-100). The width bucket is the
 request's pages rounded up to a power of two, so the attention's split count is planned for about
@@ -245,7 +246,9 @@ class StepFunction:
                     skews: tuple[int, ...] = (1,)) -> None:
         """Capture now, instead of at first use, every batch-size bucket for requests that hold between
         `from_tokens` (default: `tokens`) and `tokens` tokens (default: the widest table): every
-        block-table bucket in that range, largest first so that the smaller ones fit in its memory pool."""
+        block-table bucket in that range, largest first so that the smaller ones fit in its memory pool.
+        `skews`: the classes of steps to capture (1: requests about equally long; 2: the longest has 1.5
+        times the mean or more); a class that is not captured here is captured when a step first needs it."""
         top = self.graph_width_for(self.cache.blocks_for(tokens)) if tokens else self.graph_table_width
         if top is None:
             raise ValueError(f"{tokens} tokens are more than a captured step can hold")
