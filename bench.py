@@ -427,6 +427,61 @@ def kernel_points(model_name: str, pk: dict, with_library: bool) -> dict:
     return out
 
 
+def plan_points(model_name: str, pk: dict) -> dict:
+    """The decode attention alone over launch plans (splits, K/V stages), for requests of equal length
+    and for lengths spread evenly over 0.1..1 of the longest: microseconds of each plan, the plan that
+    `ops.decode_plan` picks knowing only the longest (`equal`) and knowing the mean too (`chosen`), and
+    the time the bytes would take at the measured copy bandwidth."""
+    import math
+    import torch
+    import layover_b200 as lb
+    from layover_b200 import ops
+
+    cfg = lb.preset(model_name)
+    d, nq, nkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ops.attention_scratch("cuda")
+    gen = torch.Generator().manual_seed(1)
+    plans = [(splits, stages) for stages in (3, 2) for splits in (1, 2, 4, 8)]
+    out = {}
+    for batch in (8, 16, 32, 64):
+        for longest in (3072, 8192):
+            for spread in ("equal", "uniform"):
+                lengths = [longest] * batch
+                if spread == "uniform":
+                    lengths = (torch.rand(batch, generator=gen) * 0.9 * longest + 0.1 * longest).int().tolist()
+                    lengths[0] = longest
+                pages_per = -(-longest // PAGE)
+                total_pages = sum(-(-n // PAGE) for n in lengths)
+                layers = max(2, min(8, int(1.5e9 // (total_pages * PAGE * nkv * d * 4))))
+                pools = torch.randn(layers, 2, total_pages + 1, nkv, PAGE, d, device="cuda").to(torch.bfloat16)
+                table = torch.zeros(batch, pages_per, dtype=torch.int32)
+                order, at = torch.randperm(total_pages, generator=gen).to(torch.int32), 0
+                for i, n in enumerate(lengths):
+                    count = -(-n // PAGE)
+                    table[i, :count] = order[at:at + count]
+                    at += count
+                table = table.cuda()
+                q = torch.randn(batch, nq * d, device="cuda").to(torch.bfloat16)
+                o = torch.empty_like(q)
+                cu = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
+                lens = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+                row = {}
+                for splits, stages in plans:
+                    t = graph_time(lambda i: ops.attention_decode_bf16(q, pools[i % layers, 0], pools[i % layers, 1], o, table, cu,
+                                                                       lens, None, batch, nq, nkv, d, PAGE, 1 / math.sqrt(d), 0,
+                                                                       splits, stages), layers)
+                    row[f"{splits}x{stages}"] = round(t * 1e3, 1)
+                mean = sum(lengths) // batch
+                row["equal"] = "%dx%d" % ops.decode_plan(batch, nq, nkv, d, longest, sms)
+                row["chosen"] = "%dx%d" % ops.decode_plan(batch, nq, nkv, d, longest, sms, mean)
+                row["bytes_us"] = round(sum(lengths) * nkv * d * 4 / pk["hbm_gbs"] / 1e3, 1)
+                out[f"b{batch}_{longest}_{spread}"] = row
+                del pools
+    torch.cuda.empty_cache()
+    return out
+
+
 def timeline_point(model, batch: int, gen) -> dict:
     """Where a replayed decode step's time goes, kernel by kernel: a torch.profiler trace of three
     replays at a context of 3,000 tokens; for one middle layer each kernel's own duration and the time
@@ -633,6 +688,8 @@ def run_ours(args) -> dict:
     pk, pk_source = peaks()
     if args.only == "kernels":
         return {"only": "kernels", **kernel_points(args.model, pk, with_library=True)}
+    if args.only == "plans":
+        return {"only": "plans", **plan_points(args.model, pk)}
     cfg = lb.preset(args.model)
     if args.layers:
         cfg = cfg.replace(num_hidden_layers=args.layers)
@@ -779,10 +836,11 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than the shape has (both numbers are reported)")
-    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "timeline"],
+    parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "timeline", "plans"],
                         help="decode or prefill alone, as a small target for a profiler; the dominant kernels alone "
-                             "with cuBLAS beside them; or one replayed decode step's time kernel by kernel (each "
-                             "prints a short line)")
+                             "with cuBLAS beside them; one replayed decode step's time kernel by kernel; or the "
+                             "decode attention over its launch plans for equal and unequal lengths (each prints a "
+                             "short line)")
     args = parser.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
