@@ -260,3 +260,24 @@ def test_a_fixed_capacity_prompt_portion():
     assert none_wanted.n_logit_rows == 0
     with pytest.raises(ValueError, match="batch of one request"):
         BatchCapacity(2, 8, portion=10)
+
+
+def test_a_batch_carries_the_contexts_its_decode_attention_plans_for():
+    """The longest and the mean context of the entries with a single token (the others are prompt
+    portions); a fixed-capacity batch takes them from the class of steps it stands for."""
+    m = manager([FULL], blocks=40, page=4, device="cpu")
+    seqs = []
+    for name, held in (("a", 30), ("b", 6), ("c", 11)):
+        seq = m.open(name)
+        m.grow(seq, held); m.commit(seq, held); m.grow(seq, held + 5)
+        seqs.append(seq)
+    builder = BatchBuilder(m, "cpu", (16,))
+    batch = builder.build([StepEntry(seqs[0], [1], [0]), StepEntry(seqs[1], [2], [0]), StepEntry(seqs[2], [3], [0])])
+    assert batch.all_decode and (batch.plan_max_ctx, batch.plan_mean_ctx) == (31, (31 + 7 + 12) // 3)
+    mixed = builder.build([StepEntry(seqs[0], [1, 2, 3, 4, 5], []), StepEntry(seqs[1], [2], [0]), StepEntry(seqs[2], [3], [0])])
+    assert not mixed.all_decode and mixed.n_decode_seqs == 2
+    assert (mixed.plan_max_ctx, mixed.plan_mean_ctx) == (12, (7 + 12) // 2)
+    capacity = BatchCapacity(4, 16)
+    buffer = torch.zeros(BatchBuilder.buffer_size(capacity, 1, (16,)), dtype=torch.int32)
+    fixed = builder.build([StepEntry(seqs[1], [2], [0])], capacity, buffer, (64, 32))
+    assert (fixed.plan_max_ctx, fixed.plan_mean_ctx) == (64, 32)
